@@ -300,6 +300,96 @@ class SSDSpec:
 
 
 @dataclass(frozen=True)
+class HeadAttentionNames:
+    """Checkpoint names of a normed attention's tensors, behind the mixer's prefix; a projection's bias is its
+    name plus ``bias``."""
+
+    q: str = "q"
+    k: str = "k"
+    v: str = "v"
+    o: str = "o"
+    q_norm: str = "q.norm"
+    k_norm: str = "k.norm"
+    gate: str = "g"
+    bias: str = ".b"
+
+
+@dataclass(frozen=True)
+class HeadAttentionSpec:
+    """Causal grouped-query attention (a *mixer*) whose q and k heads are normed (RMS over the head, one weight
+    for all heads, ``eps``) before an optional rotation of the first ``position.dim`` dims of each head (variant
+    ``"half_partial"``).  Each of the following is an option: biases on the input projections (``bias_in``) and on
+    the output projection (``bias_out``); ``values_from_keys``: there is no value projection, a token's value is its
+    key as projected (with bias, before norm and rotation); ``window`` of W: a query at p sees keys p - W + 1 .. p;
+    ``unit_sink``: the softmax's denominator has one more term of score 0 and no value; ``slope_exponent`` c: head h
+    of H takes ``2^(-c (h + 1) / H)`` times the distance to a key off its score; ``head_gate``: a head's output times
+    ``sigmoid`` of one number per head projected from the mixer's input."""
+
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    key_dim: int
+    value_dim: int
+    softmax_scale: float
+    eps: float
+    qk_norm: bool = True
+    position: Optional[RotarySpec] = None
+    window: Optional[int] = None
+    unit_sink: bool = False
+    slope_exponent: Optional[float] = None
+    head_gate: bool = False
+    values_from_keys: bool = False
+    bias_in: bool = False
+    bias_out: bool = False
+    names: HeadAttentionNames = HeadAttentionNames()
+    kind: str = "head_attention"
+
+
+@dataclass(frozen=True)
+class DeltaRuleNames:
+    """Checkpoint names of a gated delta rule's tensors, behind the mixer's prefix; a filter's tensor is its
+    projection's name plus ``conv``."""
+
+    q: str = "q"
+    k: str = "k"
+    v: str = "v"
+    conv: str = ".conv"
+    beta: str = "b"
+    a_log: str = "A_log"
+    decay_down: str = "a1"
+    decay_up: str = "a2"
+    dt_bias: str = "dt_bias"
+    gate_down: str = "g1"
+    gate_up: str = "g2"
+    norm: str = "norm"
+    o: str = "o"
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """Gated delta rule (a recurrent *mixer*): per head a state ``S [key_dim, value_dim]``, per token ``S <- diag(g)
+    S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``.  q, k (``kv_heads`` heads of ``key_dim``) and v (``heads`` of
+    ``value_dim``) pass a causal filter of ``conv_taps`` taps per channel and silu; q and k become unit vectors per head
+    (``x / sqrt(sum x^2 + 1e-6)``), q also times ``key_dim ** -0.5``; ``beta = sigmoid(W_b h)`` per head; ``g =
+    exp(-exp(A_log_h) softplus(W_a2 W_a1 h + dt_bias))`` per head and key channel; the read-out is divided by its
+    root mean square over ``value_dim`` (``norm_eps``), times a weight ``[value_dim]``, times ``sigmoid(W_g2 W_g1
+    h)``.  ``decay_rank`` / ``gate_rank`` are the inner sizes of the two low-rank projections; None: whatever the
+    checkpoint's tensors have (random weights then take ``key_dim // 2`` rounded up to 8)."""
+
+    hidden: int
+    heads: int
+    kv_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    norm_eps: float
+    decay_rank: Optional[int] = None
+    gate_rank: Optional[int] = None
+    names: DeltaRuleNames = DeltaRuleNames()
+    kind: str = "gated_delta"
+
+
+@dataclass(frozen=True)
 class MixerBranch:
     """One of the mixers of a ``ParallelMixerSpec``: its spec, the prefix of its tensors behind the parallel
     mixer's own, and the constant its output is multiplied with."""
@@ -373,7 +463,7 @@ class LayerSpec:
     feed_forward_norm: object
     mixer_norm_prefix: str
     feed_forward_norm_prefix: str
-    kind: str = "prenorm"
+    kind: str = "prenorm"           # "parallel_residual": h += mixer(norm1(h)) + feed_forward(norm2(h)), both norms of the same h
 
 
 @dataclass(frozen=True)

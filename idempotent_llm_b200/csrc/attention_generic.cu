@@ -28,6 +28,8 @@ struct AttnArgs {
     const float* gate; int gate_stride;   // or null: out *= sigmoid(gate[t * gate_stride + head * dv + d])
     int out_stride, out_col;      // out[t * out_stride + out_col + head * dv + d]
     float out_scale;
+    const float* slopes;          // [n_q] or null: slopes[head] * (p - j) is taken off the score of key j
+    int gate_per_head;            // the gate is one number per head: gate[t * gate_stride + head]
 };
 
 #define AG_WARPS 4
@@ -78,6 +80,7 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(AttnAr
                 for (int d = 0; d < a.hd; ++d) dot = fmaf(qs[d], to_f32(krow[d]), dot);
             }
             sc = dot * a.scale;
+            if (a.slopes) sc -= a.slopes[head] * (float)(pos - j);
         }
         const float m_new = fmaxf(m, warp_max(sc));
         const float alpha = expf(m - m_new);
@@ -100,12 +103,13 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(AttnAr
     }
     T* orow = a.out + (size_t)t * a.out_stride + a.out_col + (size_t)head * a.dv;
     const float inv = 1.0f / l;
-    const float* grow = a.gate ? a.gate + (size_t)t * a.gate_stride + (size_t)head * a.dv : nullptr;
+    const float* grow = a.gate && !a.gate_per_head ? a.gate + (size_t)t * a.gate_stride + (size_t)head * a.dv : nullptr;
+    const float head_gate = a.gate && a.gate_per_head ? 1.0f / (1.0f + expf(-a.gate[(size_t)t * a.gate_stride + head])) : 1.f;
 #pragma unroll
     for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) {
         const int d = lane + 32 * i;
         if (d < a.dv) {
-            float o = acc[i] * inv;
+            float o = acc[i] * inv * head_gate;
             if (grow) o = o / (1.0f + expf(-grow[d]));
             if (a.out_scale != 1.f) o *= a.out_scale;
             from_f32(orow[d], o);
@@ -139,6 +143,7 @@ extern "C" int idm_attention_generic(const void* q, void* out, void* k_pool, voi
     a.token_seq = token_seq; a.positions = positions; a.slots = slots; a.q_start = q_start; a.cu_q = cu_q;
     a.n_tokens = n_tokens; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd; a.scale = scale; a.window = window;
     a.dv = hd; a.sink = nullptr; a.gate = nullptr; a.gate_stride = 0; a.out_stride = n_q * hd; a.out_col = 0; a.out_scale = 1.f;
+    a.slopes = nullptr; a.gate_per_head = 0;
     return attention_generic_launch(a, stream);
 }
 
@@ -166,5 +171,32 @@ extern "C" int idm_attention_sink(const void* q, void* out, int out_stride, int 
     a.n_tokens = n_tokens; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd; a.scale = scale; a.window = window;
     a.dv = dv; a.sink = sink; a.gate = gate; a.gate_stride = gate_stride; a.out_stride = out_stride; a.out_col = out_col;
     a.out_scale = out_scale;
+    a.slopes = nullptr; a.gate_per_head = 0;
+    return attention_generic_launch(a, stream);
+}
+
+// The same walk once more with every option this kernel has: a window over a cache that keeps all keys (ring 0) or
+// a ring, a sink, a slope per head whose product with the distance p - j is taken off the score, and a gate that is
+// one number per head (gate_per_head) or one per channel.
+extern "C" int idm_attention_biased(const void* q, void* out, int out_stride, int out_col, float out_scale,
+                                    void* k_pool, void* v_pool, const int* table, int table_stride, int ring,
+                                    const float* sink, const float* slopes, const float* gate, int gate_stride,
+                                    int gate_per_head, const int* token_seq, const int* positions, const int* slots,
+                                    const int* q_start, const int* cu_q, int n_tokens, int n_q, int n_kv,
+                                    int hd, int dv, float scale, int window, cudaStream_t stream) {
+    if (n_tokens == 0) return 0;
+    IDM_REQUIRE(hd > 0 && hd <= IDM_MAX_HEAD_DIM && dv > 0 && dv <= IDM_MAX_HEAD_DIM,
+                "attention: key and value sizes %d, %d must be at most %d", hd, dv, IDM_MAX_HEAD_DIM);
+    IDM_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "attention: %d q-heads are no multiple of %d kv-heads", n_q, n_kv);
+    IDM_REQUIRE(out_col >= 0 && out_col + n_q * dv <= out_stride, "attention: columns %d..%d of rows of %d", out_col,
+                out_col + n_q * dv, out_stride);
+    AttnArgs a;
+    a.q = (const T*)q; a.out = (T*)out;
+    a.cache = KVAddr{(T*)k_pool, (T*)v_pool, table, table_stride, ring, n_kv, hd};
+    a.k_new = nullptr; a.v_new = nullptr;
+    a.token_seq = token_seq; a.positions = positions; a.slots = slots; a.q_start = q_start; a.cu_q = cu_q;
+    a.n_tokens = n_tokens; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd; a.scale = scale; a.window = window;
+    a.dv = dv; a.sink = sink; a.gate = gate; a.gate_stride = gate_stride; a.out_stride = out_stride; a.out_col = out_col;
+    a.out_scale = out_scale; a.slopes = slopes; a.gate_per_head = gate_per_head;
     return attention_generic_launch(a, stream);
 }

@@ -158,6 +158,55 @@ extern "C" int idm_add_rmsnorm(float* h, const float* delta, int n_partials, lon
     return 0;
 }
 
+// Two norms of the same row with one pass over it, for layers whose mixer and feed-forward both read the stream
+// as it stands: h[r] += sum_p delta[p][r] (stored), x1 = norm(h[r]) * gamma1, x2 = norm(h[r]) * gamma2 (null: the
+// layer has no second reader); the root mean square is taken once.  `post`, if given, is a constant row added to
+// the stream AFTER the norms are taken (a bias of the layer's output that does not depend on its input), so
+// that no pass of its own has to add it.
+__global__ void __launch_bounds__(256) add_rmsnorm2_kernel(float* __restrict__ h, const float* __restrict__ delta, int n_partials,
+                                                           size_t partial_stride, const float* __restrict__ gamma1,
+                                                           const float* __restrict__ gamma2, float eps, T* __restrict__ x1,
+                                                           T* __restrict__ x2, const float* __restrict__ post, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    extern __shared__ float vals[];
+    const int r = blockIdx.x;
+    float* hr = h + (size_t)r * hidden;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float v = add_partials(hr[c], delta, n_partials, partial_stride, (size_t)r * hidden + c);
+        if (n_partials || post) hr[c] = post ? v + post[c] : v;
+        vals[c] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    T* xr1 = x1 + (size_t)r * hidden;
+    T* xr2 = x2 ? x2 + (size_t)r * hidden : nullptr;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float n = vals[c] * inv;
+        from_f32(xr1[c], n * gamma1[c]);
+        if (xr2) from_f32(xr2[c], n * gamma2[c]);
+    }
+}
+
+extern "C" int idm_add_rmsnorm2(float* h, const float* delta, int n_partials, long long partial_stride,
+                                const float* gamma1, const float* gamma2, float eps, void* x1, void* x2,
+                                const float* post, int n_rows, int hidden, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    IDM_REQUIRE(hidden > 0 && n_rows > 0, "add_rmsnorm2: bad sizes rows=%d hidden=%d", n_rows, hidden);
+    IDM_REQUIRE((size_t)hidden * 4 <= 160 * 1024, "add_rmsnorm2: hidden=%d does not fit shared memory", hidden);
+    IDM_REQUIRE((gamma2 == nullptr) == (x2 == nullptr), "add_rmsnorm2: a second weight and a second output come together");
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(add_rmsnorm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    idm_launch(add_rmsnorm2_kernel, dim3(n_rows), dim3(256), smem, stream, h, delta, delta ? n_partials : 0,
+               (size_t)partial_stride, gamma1, gamma2, eps, (T*)x1, (T*)x2, post, hidden);
+    IDM_LAUNCH_CHECK("add_rmsnorm2");
+    return 0;
+}
+
 // ---------------------------------------------------------------- rotary table
 // cs[t, j] = (cos, sin)(positions[t] * inv_freq[j]), angle and functions in 64-bit,
 // rounded to 32-bit (src/detllm/ops/rope.py:25-35 builds its table the same way).

@@ -69,6 +69,13 @@ SIGNATURES = {
     "idm_ssd_scan": (c_int, "piiiipiiippppqpippiiiiippipip"),
     "idm_ssd_group_norm": (c_int, "piipffpiiip"),
     "idm_attention_sink": (c_int, "ppiifpppippipppppiiiiifip"),
+    "idm_attention_biased": (c_int, "ppiifpppiipppiipppppiiiiifip"),
+    "idm_head_finish": (c_int, "piiiipppppfipfiiiippppiipppip"),
+    "idm_cols_cast": (c_int, "piiipiip"),
+    "idm_delta_prep": (c_int, "piiipiipiipppiiiip"),
+    "idm_delta_scan": (c_int, "piiiipiippqpippiiiiip"),
+    "idm_delta_out": (c_int, "pipfpiifpiiiiip"),
+    "idm_add_rmsnorm2": (c_int, "ppiqppfpppiip"),
     "idm_gemm_bf16_gated": (c_int, "pppiiiip"),
     "idm_add_rmsnorm": (c_int, "ppiqpfppiip"),
     "idm_rope_table": (c_int, "ppppiip"),
@@ -383,6 +390,96 @@ class Kernels:
             kv.table.shape[1], _p(sink), (gate.data_ptr() if gate is not None else None), gate_stride,
             _p(ctx.token_seq), _p(ctx.positions), _p(ctx.slots), _p(ctx.q_start), _p(ctx.cu_q), n, n_q,
             kv.n_kv_heads, dk, dv, scale, 0, self._stream()))
+
+    def attention_biased(self, q, kv, ctx, scale: float, out, out_col: int, out_scale: float = 1.0, sink=None,
+                         slopes=None, gate=None, gate_stride: int = 0, gate_per_head: bool = False, window=None) -> None:
+        """The general attention kernel with all of its options: ``sink`` [n_q] joins the denominator, ``slopes`` [n_q]
+        times the distance to a key is taken off its score, ``window`` keys are seen, the result is multiplied by
+        ``sigmoid(gate)`` (one number per head at ``gate[t, head]`` or one per channel) and by ``out_scale`` and
+        stored at columns ``out_col ..`` of ``out``."""
+        n, n_q, dk = q.shape
+        self._check_kv(kv, kv.n_kv_heads, dk, kv.v_head_dim)
+        for name, t in (("sink", sink), ("slopes", slopes)):
+            if t is not None and (t.dtype != torch.float32 or t.numel() != n_q):
+                raise KernelError(f"attention: {name} must hold one 32-bit number per head")
+        self._check(self.lib.idm_attention_biased(
+            _p(q), _p(out), out.shape[1], out_col, float(out_scale), _p(kv.k), _p(kv.v), _p(kv.table), kv.table.shape[1],
+            kv.ring, _p(sink), _p(slopes), _p(gate), gate_stride, 1 if gate_per_head else 0, _p(ctx.token_seq),
+            _p(ctx.positions), _p(ctx.slots), _p(ctx.q_start), _p(ctx.cu_q), n, n_q, kv.n_kv_heads, dk, kv.v_head_dim,
+            float(scale), int(window) if window else 0, self._stream()))
+
+    def head_finish(self, proj, col_q: int, col_k: int, col_v, n_q: int, n_kv: int, dk: int, dv: int, biases, gammas,
+                    eps: float, cs, mag: float, kv, ctx) -> torch.Tensor:
+        """Bias, norm per head and partial rotation of the q and k heads in columns of the 32-bit ``proj``; k and v to
+        the cache entry (``col_v`` None: the keys as projected are the values); returns q ``[N, n_q, dk]``."""
+        self._need(proj, torch.float32, "projection")
+        n, width = proj.shape
+        self._check_kv(kv, n_kv, dk, dv)
+        half = 0 if cs is None else cs.shape[1]
+        if cs is not None and (cs.dtype != torch.float32 or tuple(cs.shape) != (n, half, 2)):
+            raise KernelError(f"rotary table {tuple(cs.shape)} does not match {(n, half, 2)}")
+        bq, bk, bv = biases
+        gq, gk = gammas
+        q = torch.empty((n, n_q, dk), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_head_finish(
+            _p(proj), width, col_q, col_k, -1 if col_v is None else col_v, _p(bq), _p(bk), _p(bv), _p(gq), _p(gk),
+            float(eps), half, _p(cs), float(mag), n_q, n_kv, dk, dv, _p(q), _p(kv.k), _p(kv.v), _p(kv.table),
+            kv.table.shape[1], kv.ring, _p(ctx.token_seq), _p(ctx.positions), _p(ctx.slots), n, self._stream()))
+        return q
+
+    def cols_cast(self, proj, col0: int, width: int, out_width: int) -> torch.Tensor:
+        """Columns ``[col0, col0 + width)`` of a 32-bit buffer as a matrix operand ``[N, out_width]`` in the storage
+        type, zero beyond ``width``."""
+        self._need(proj, torch.float32, "projection")
+        n = proj.shape[0]
+        out = torch.empty((n, out_width), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_cols_cast(_p(proj), proj.shape[1], col0, width, _p(out), out_width, n, self._stream()))
+        return out
+
+    def delta_prep(self, c, c_q: int, c_k: int, a, a_col: int, proj, b_col: int, dt_bias, a_log, H: int, Hk: int,
+                   dk: int) -> torch.Tensor:
+        """In place: q and k heads of ``c`` become unit vectors (q times ``dk ** -0.5``), columns ``a_col ..`` of ``a``
+        become decays; returns ``beta [N, H]``."""
+        n = c.shape[0]
+        beta = torch.empty((n, H), dtype=torch.float32, device=self.device)
+        self._check(self.lib.idm_delta_prep(_p(c), c.shape[1], c_q, c_k, _p(a), a.shape[1], a_col, _p(proj), proj.shape[1],
+                                            b_col, _p(dt_bias), _p(a_log), _p(beta), H, Hk, dk, n, self._stream()))
+        return beta
+
+    def delta_scan(self, c, c_q: int, c_k: int, c_v: int, g, g_col: int, beta, state, ctx, H: int, Hk: int, dk: int,
+                   dv: int) -> torch.Tensor:
+        """The gated delta rule over the step's tokens from and to each sequence's state ``[slots, H * dv * dk]``;
+        returns the read-outs ``[N, H * dv]`` in 32-bit."""
+        n = c.shape[0]
+        o = torch.empty((n, H * dv), dtype=torch.float32, device=self.device)
+        self._check(self.lib.idm_delta_scan(_p(c), c.shape[1], c_q, c_k, c_v, _p(g), g.shape[1], g_col, _p(beta), _p(state),
+                                            self._state_stride(state), _p(o), H * dv, _p(ctx.cu_q), _p(ctx.slots),
+                                            ctx.n_seqs, H, Hk, dk, dv, self._stream()))
+        return o
+
+    def delta_out(self, o, w, eps: float, gate, gate_col: int, scale: float, out, out_col: int, H: int, dv: int) -> None:
+        """``out[:, out_col ..] = rmsnorm over each head of o * w * sigmoid(gate columns) * scale``."""
+        n = o.shape[0]
+        self._check(self.lib.idm_delta_out(_p(o), o.shape[1], _p(w), float(eps), _p(gate), gate.shape[1], gate_col,
+                                           float(scale), _p(out), out.shape[1], out_col, n, H, dv, self._stream()))
+
+    def add_rmsnorm2(self, h, delta, gamma1, gamma2, eps: float, post=None):
+        """``h += delta`` in place, then both norms of the same row from one root mean square: returns ``(norm(h) *
+        gamma1, norm(h) * gamma2)`` (the second None without ``gamma2``); ``post`` [hidden] is added to the stream
+        after the norms were taken."""
+        self._need(h, torch.float32, "residual stream")
+        n, hidden = h.shape
+        P, stride = 0, 0
+        if delta is not None:
+            self._need(delta, torch.float32, "delta")
+            if delta.dim() != 3 or tuple(delta.shape[1:]) != (n, hidden):
+                raise KernelError(f"delta {tuple(delta.shape)} does not match the stream {(n, hidden)}")
+            P, stride = delta.shape[0], n * hidden
+        x1 = torch.empty((n, hidden), dtype=self.dtype, device=self.device)
+        x2 = torch.empty((n, hidden), dtype=self.dtype, device=self.device) if gamma2 is not None else None
+        self._check(self.lib.idm_add_rmsnorm2(_p(h), _p(delta), P, stride, _p(gamma1), _p(gamma2), float(eps), _p(x1),
+                                              _p(x2), _p(post), n, hidden, self._stream()))
+        return x1, x2
 
     def gemm_gated(self, x, w_tiled, inter: int, act: int) -> torch.Tensor:
         """``act(x . gate^T) * (x . up^T)`` in the storage dtype ``[M, inter]`` (``tile_gate_up`` layout)."""

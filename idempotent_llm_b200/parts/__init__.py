@@ -13,8 +13,12 @@ from .parallel import ParallelMixer
 from .sandwich import SandwichBlock, TokenSide
 from .latent_attention import LatentAttention
 from .experts import TableExperts
+from .head_attention import HeadAttention
+from .delta_rule import GatedDeltaRule
+from .parallel_block import ParallelResidualBlock
 
 __all__ = ["BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITIONS", "Block", "FeedForward", "Mixer",
            "Norm", "NormedDelta", "Part", "PositionEncoding", "Runtime", "RMSNorm", "Rotary", "GQAAttention",
            "GatedMLP", "PreNormBlock", "SinkAttention", "SSDMixer", "ParallelMixer", "SandwichBlock", "TokenSide",
-           "DyT", "DenseMLP", "LatentAttention", "TableExperts"]
+           "DyT", "DenseMLP", "LatentAttention", "TableExperts", "HeadAttention", "GatedDeltaRule",
+           "ParallelResidualBlock"]

@@ -1,0 +1,122 @@
+"""Gated delta rule (a recurrent mixer).
+
+In this file's notation, for the mixer's input h_t, with H heads of value size P, Hk key heads of size D:
+
+    q, k, v   = silu(filter(Wq h)), silu(filter(Wk h)), silu(filter(Wv h))     per channel, ``conv_taps`` taps, causal
+    q, k     <- q / sqrt(|q|^2 + 1e-6) * D^-1/2,  k / sqrt(|k|^2 + 1e-6)        per head
+    beta_t    = sigmoid(Wb h_t)                                                 per head
+    g_t       = exp(-exp(A_log) * softplus(Wa2 (Wa1 h_t) + dt_bias))            per head and key channel
+    S        <- diag(g_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T      S: [D, P] per head, head i reads key head i // (H / Hk)
+    y_t       = S^T q_t
+    o_t       = y_t / sqrt(mean(y_t^2) + eps) * w * sigmoid(Wg2 (Wg1 h_t))      per head; w [P] for all heads
+    out       = Wo o_t
+
+The recurrence, its decays, step sizes and gates, the unit norms and the norm behind it run in 32-bit.  Per-sequence
+state: the filters' last ``conv_taps - 1`` inputs and S, in 32-bit, zero at a sequence's start.  The two low-rank
+projections' second halves are one product with the two matrices on the diagonal of one.
+
+Alone (``forward``) or as a branch of a parallel mixer (``in_weight`` / ``out_weight`` / ``inner`` / ``mix``).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache.spec import CacheNeed
+from ..weights.loader import TensorDecl
+from .base import MIXERS, Mixer
+
+
+def _default_rank(s) -> int:
+    return max(8, -(-(s.key_dim // 2) // 8) * 8)
+
+
+@MIXERS.register("gated_delta")
+class GatedDeltaRule(Mixer):
+    @staticmethod
+    def _sizes(s):
+        qk, v = s.kv_heads * s.key_dim, s.heads * s.value_dim
+        return qk, v, 2 * qk + v                    # one of q / k, v, filtered channels
+
+    @classmethod
+    def declare(cls, spec, prefix):
+        s, nm = spec, spec.names
+        qk, v, ch = cls._sizes(s)
+        ra = s.decay_rank if s.decay_rank is not None else -1
+        rg = s.gate_rank if s.gate_rank is not None else -1
+        free = _default_rank(s)
+        rows = [(nm.q, qk), (nm.k, qk), (nm.v, v)]
+        d = [TensorDecl(prefix + n, (r, s.hidden)) for n, r in rows]
+        if s.conv_taps > 1:
+            d += [TensorDecl(prefix + n + nm.conv, (r, s.conv_taps), init="filter") for n, r in rows]
+        d += [TensorDecl(prefix + nm.beta, (s.heads, s.hidden)),
+              TensorDecl(prefix + nm.a_log, (s.heads,), init="unit_normal"),
+              TensorDecl(prefix + nm.norm, (s.value_dim,), init="one_plus_normal"),
+              TensorDecl(prefix + nm.decay_down, (ra, s.hidden), free=free),
+              TensorDecl(prefix + nm.decay_up, (s.heads * s.key_dim, ra), free=free),
+              TensorDecl(prefix + nm.dt_bias, (s.heads * s.key_dim,), init="unit_normal"),
+              TensorDecl(prefix + nm.gate_down, (rg, s.hidden), free=free),
+              TensorDecl(prefix + nm.gate_up, (v, rg), free=free),
+              TensorDecl(prefix + nm.o, (s.hidden, v))]
+        return d
+
+    @classmethod
+    def cache_need(cls, spec) -> CacheNeed:
+        s = spec
+        qk, v, ch = cls._sizes(s)
+        return CacheNeed(kind="none", state_shape=((s.conv_taps - 1) * ch + s.heads * s.key_dim * s.value_dim,))
+
+    def __init__(self, spec, weights, prefix, rt):
+        s, nm = spec, spec.names
+        if s.heads % s.kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        qk, v, ch = self._sizes(s)
+        self.spec, self.rt = spec, rt
+        self.qk, self.inner, self.channels = qk, v, ch
+        a1, a2 = weights[prefix + nm.decay_down], weights[prefix + nm.decay_up]
+        g1, g2 = weights[prefix + nm.gate_down], weights[prefix + nm.gate_up]
+        ra, rg = a1.shape[0], g1.shape[0]
+        if a2.shape[1] != ra or g2.shape[1] != rg:
+            raise ValueError(f"{prefix}: the halves of a low-rank projection disagree on its inner size "
+                             f"({ra} / {a2.shape[1]}, {rg} / {g2.shape[1]})")
+        self.ranks = (ra, rg)
+        mats = [weights[prefix + n] for n in (nm.q, nm.k, nm.v, nm.beta)] + [a1, g1]
+        self.in_weight = torch.cat([m.to(rt.dtype) for m in mats], dim=0).contiguous()
+        self.out_weight = weights[prefix + nm.o].to(rt.dtype).contiguous()
+        self.col_beta = ch
+        self.col_low = ch + s.heads
+        # the second halves of both low-rank projections as one matrix: [decay rows | gate rows] x [ra | rg], zero
+        # elsewhere, its inner size rounded up to 8 (rows on 16-byte borders in bfloat16)
+        self.low_width = -(-(ra + rg) // 8) * 8
+        up = torch.zeros((s.heads * s.key_dim + v, self.low_width), dtype=rt.dtype, device=rt.device)
+        up[:s.heads * s.key_dim, :ra] = a2.to(rt.dtype)
+        up[s.heads * s.key_dim:, ra:ra + rg] = g2.to(rt.dtype)
+        self.up_weight = up
+        f32 = lambda n: weights[prefix + n].to(torch.float32).contiguous()
+        if s.conv_taps > 1:
+            self.w_conv = torch.cat([f32(n + nm.conv) for n in (nm.q, nm.k, nm.v)], dim=0).contiguous()
+        else:
+            self.w_conv = torch.ones((ch, 1), dtype=torch.float32, device=rt.device)
+        self.dt_bias, self.a_log, self.norm = f32(nm.dt_bias), f32(nm.a_log), f32(nm.norm)
+        self.conv_floats = (s.conv_taps - 1) * ch
+
+    def mix(self, proj, col0, ctx, kv, state, out, out_col, out_scale):
+        s, K = self.spec, self.rt.kernels
+        conv_state = state[:, :self.conv_floats] if self.conv_floats else None
+        c = K.short_conv(proj, col0, self.channels, self.w_conv, None, 1, conv_state, ctx)      # [q | k | v], silu
+        if s.conv_taps > 1 and not ctx.single_token:
+            K.conv_state_update(proj, col0, self.channels, s.conv_taps, conv_state, ctx)
+        low = K.cols_cast(proj, col0 + self.col_low, sum(self.ranks), self.low_width)
+        ag = K.gemm_store(low, self.up_weight)                                                  # [decay | gate], 32-bit
+        beta = K.delta_prep(c, 0, self.qk, ag, 0, proj, col0 + self.col_beta, self.dt_bias, self.a_log, s.heads,
+                            s.kv_heads, s.key_dim)
+        y = K.delta_scan(c, 0, self.qk, 2 * self.qk, ag, 0, beta, state[:, self.conv_floats:], ctx, s.heads, s.kv_heads,
+                         s.key_dim, s.value_dim)
+        K.delta_out(y, self.norm, s.norm_eps, ag, s.heads * s.key_dim, out_scale, out, out_col, s.heads, s.value_dim)
+
+    def forward(self, x, ctx, kv, state, writes_cache: bool):
+        K = self.rt.kernels
+        proj = K.gemm_store(x, self.in_weight, pad=True)
+        out = torch.empty((x.shape[0], self.inner), dtype=self.rt.dtype, device=x.device)
+        self.mix(proj, 0, ctx, None, state, out, 0, 1.0)
+        return K.gemm(out, self.out_weight, pad=True)

@@ -9,6 +9,11 @@ branches' output matrices side by side is the weighted sum.  A branch therefore 
     out_weight [hidden, inner]    its output projection
     inner                         columns of its activations
     mix(proj, col0, ctx, kv, state, out, out_col, out_scale)
+    out_bias                      optional: a 32-bit row [hidden] its output projection adds
+
+The branches' biases, each times its branch's constant, are one constant row ``stream_bias``.  A block that knows of
+it adds it to the stream itself (``bias_in_stream=True``); for any other caller the mixer adds it to its delta.  Given
+``residual``, the output product adds into the stream in its epilogue where the kernels can.
 
 What the branches keep is merged into one cache entry: the keys and values of the one branch that has some,
 and one per-sequence state region in which every branch has its own columns.
@@ -35,6 +40,8 @@ def _state_floats(need: CacheNeed) -> int:
 
 @MIXERS.register("parallel")
 class ParallelMixer(Mixer):
+    accepts_residual = True
+
     @classmethod
     def declare(cls, spec, prefix):
         d = []
@@ -75,8 +82,15 @@ class ParallelMixer(Mixer):
         for p in self.branches:                     # the joint matrices are the ones that are read
             p.in_weight = p.out_weight = None
         self.graph_safe = all(getattr(p, "graph_safe", True) for p in self.branches)
+        self.stream_bias = None
+        for p, scale in zip(self.branches, self.scales):
+            b = getattr(p, "out_bias", None)
+            if b is not None:
+                b = b.to(torch.float32) * scale
+                self.stream_bias = b if self.stream_bias is None else self.stream_bias + b
+        self._aligned = spec.hidden % 8 == 0 and self.inner % 8 == 0
 
-    def forward(self, x, ctx, kv, state, writes_cache: bool):
+    def forward(self, x, ctx, kv, state, writes_cache: bool, residual=None, bias_in_stream: bool = False):
         K = self.rt.kernels
         proj = K.gemm_store(x, self.in_weight, pad=True)                       # 32-bit [N, all branches' rows]
         out = torch.empty((x.shape[0], self.inner), dtype=self.rt.dtype, device=x.device)
@@ -85,4 +99,11 @@ class ParallelMixer(Mixer):
             p.mix(proj, col0, ctx, kv, state[:, a:b] if b > a else None, out, out_col, scale)
             col0 += rows
             out_col += p.inner
-        return K.gemm(out, self.out_weight, pad=True)                          # [1, N, hidden]
+        add_bias = self.stream_bias is not None and not bias_in_stream
+        if residual is not None and getattr(K, "fused", False) and self._aligned and not add_bias:
+            K.gemm_residual(out, self.out_weight, residual)
+            return None
+        delta = K.gemm(out, self.out_weight, pad=True)                         # [1, N, hidden]
+        if add_bias:
+            delta += self.stream_bias
+        return delta

@@ -77,6 +77,8 @@ def _register_builtin() -> None:
     register_architecture(LUNULIX, LunulixConfig)
     from .config.panodra import ARCHITECTURE as PANODRA, PanodraConfig
     register_architecture(PANODRA, PanodraConfig)
+    from .config.fuginex import ARCHITECTURE as FUGINEX, FuginexConfig
+    register_architecture(FUGINEX, FuginexConfig)
 
 
 _register_builtin()

@@ -30,7 +30,8 @@ class TensorDecl:
     (``normal``: N(0, std); ``one_plus_normal``: 1 + N(0, std), for norm weights; ``filter`` and
     ``unit_normal``: N(0, 0.5), for a short filter's taps and per-head constants; ``half_plus_normal``: 0.5 + N(0, 0.1);
     ``choices``: an integer table whose rows hold distinct numbers below ``high``).  ``integer``: the tensor is a
-    table of integers (kept as int32), not floating point."""
+    table of integers (kept as int32), not floating point.  An entry of ``shape`` that is -1 is a size the checkpoint
+    decides (a low-rank projection's inner size); random init takes ``free`` there."""
 
     name: str
     shape: Tuple[int, ...]
@@ -38,6 +39,7 @@ class TensorDecl:
     optional: bool = False   # present-or-absent both fine (an lm_head beside tied embeddings)
     integer: bool = False
     high: int = 0
+    free: int = 0
 
 
 class WeightError(ValueError):
@@ -76,7 +78,7 @@ def check_declared(where: str, decls: Sequence[TensorDecl], have: Dict[str, Tupl
     for n, d in want.items():
         if n in have:
             dt, shape = have[n]
-            if tuple(shape) != tuple(d.shape):
+            if len(shape) != len(d.shape) or any(w != -1 and g != w for g, w in zip(shape, d.shape)):
                 wrong_shape.append((n, tuple(shape), tuple(d.shape)))
             if not isinstance(dt, torch.dtype) or dt.is_floating_point == d.integer or dt == torch.bool:
                 wrong_dtype.append((n, dt))

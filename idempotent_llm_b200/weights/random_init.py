@@ -29,7 +29,8 @@ def draw(decl: TensorDecl, seed: int, std: float, dtype: torch.dtype, device="cp
     if decl.init == "choices":          # every row: distinct integers below `high`, in random order
         rows, top = decl.shape
         return torch.rand((rows, decl.high), generator=g, device=device).argsort(dim=1)[:, :top].to(torch.int32).contiguous()
-    t = torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device)
+    shape = tuple(decl.free if n == -1 else n for n in decl.shape)      # a size the checkpoint decides: the declared default
+    t = torch.randn(shape, generator=g, dtype=torch.float32, device=device)
     if decl.init in ("filter", "unit_normal"):
         t = t * 0.5             # taps of a short filter, per-head constants: of order one whatever `std` is
     else:
