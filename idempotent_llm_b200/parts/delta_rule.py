@@ -47,8 +47,7 @@ class GatedDeltaRule(Mixer):
         free = _default_rank(s)
         rows = [(nm.q, qk), (nm.k, qk), (nm.v, v)]
         d = [TensorDecl(prefix + n, (r, s.hidden)) for n, r in rows]
-        if s.conv_taps > 1:
-            d += [TensorDecl(prefix + n + nm.conv, (r, s.conv_taps), init="filter") for n, r in rows]
+        d += [TensorDecl(prefix + n + nm.conv, (r, s.conv_taps), init="filter") for n, r in rows]    # (one tap: a factor)
         d += [TensorDecl(prefix + nm.beta, (s.heads, s.hidden)),
               TensorDecl(prefix + nm.a_log, (s.heads,), init="unit_normal"),
               TensorDecl(prefix + nm.norm, (s.value_dim,), init="one_plus_normal"),
@@ -93,10 +92,7 @@ class GatedDeltaRule(Mixer):
         up[s.heads * s.key_dim:, ra:ra + rg] = g2.to(rt.dtype)
         self.up_weight = up
         f32 = lambda n: weights[prefix + n].to(torch.float32).contiguous()
-        if s.conv_taps > 1:
-            self.w_conv = torch.cat([f32(n + nm.conv) for n in (nm.q, nm.k, nm.v)], dim=0).contiguous()
-        else:
-            self.w_conv = torch.ones((ch, 1), dtype=torch.float32, device=rt.device)
+        self.w_conv = torch.cat([f32(n + nm.conv) for n in (nm.q, nm.k, nm.v)], dim=0).contiguous()
         self.dt_bias, self.a_log, self.norm = f32(nm.dt_bias), f32(nm.a_log), f32(nm.norm)
         self.conv_floats = (s.conv_taps - 1) * ch
 

@@ -285,3 +285,116 @@ def make_panodra_dir(cfg: dict, out_dir: str, seed: int = 1, dtype=torch.bfloat1
 
 
 read_model_dir = read_lunulix        # (config dict, tensors by name) of any model folder
+
+
+# ------------------------------------------------------------------------------------- Fuginex
+def fuginex_parallel(heads=4, kv_heads=2, dim=16, scale=0.3, window=20, rot_dims=8, rot_base=5000.0,
+                     scaling=(4.0, 64, 8.0, 1.0), r_heads=4, r_kv_heads=2, r_dim=12, r_vdim=20, conv=3, ranks=(8, 16),
+                     left_scale=1.2, right_scale=0.9, ff=48, weights_of=None):
+    """One ``parallel`` layer of a Fuginex config.json; every size and constant is an argument.  ``scaling``: (factor,
+    original, fast, slow) or None; ``ranks``: the two low-rank sizes, or None to leave them to the tensors."""
+    left = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=scale)
+    if window:
+        left["mask"] = dict(size=window)
+    if rot_dims:
+        left["rot"] = dict(base=rot_base, dims=rot_dims)
+        if scaling:
+            left["rot"]["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    right = dict(heads=r_heads, kv_heads=r_kv_heads, dim=r_dim, vdim=r_vdim, conv=conv)
+    if ranks:
+        right["decay_rank"], right["gate_rank"] = ranks
+    L = dict(type="parallel", mixer=dict(left=left, right=right, left_scale=left_scale, right_scale=right_scale),
+             mlp=None if ff is None else dict(kind="dense", ff=ff))
+    if weights_of is not None:
+        L["weights_of"] = weights_of
+    return L
+
+
+def fuginex_attention(heads=4, kv_heads=2, dim=24, vdim=16, scale=0.25, ff=40, weights_of=None):
+    L = dict(type="attention", mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale),
+             mlp=None if ff is None else dict(kind="dense", ff=ff))
+    if weights_of is not None:
+        L["weights_of"] = weights_of
+    return L
+
+
+def fuginex_config(layers, vocab=97, width=32, eps=1e-5):
+    import copy
+    layers = [copy.deepcopy(L) for L in layers]
+    for L in layers:                              # a layer that borrows tensors repeats its owner's entry
+        if L.get("weights_of") is not None:
+            o = layers[L["weights_of"]]
+            L.update(type=o["type"], mixer=copy.deepcopy(o["mixer"]), mlp=copy.deepcopy(o["mlp"]))
+    return dict(architecture="Fuginex", vocab=vocab, width=width, norm=dict(eps=eps), layers=layers)
+
+
+# Small Fuginex models that differ from one another in every size and option.
+FUGINEX = {
+    # both kinds of layer, two layers run again with the first ones' tensors (in another order than they came),
+    # a window shorter than a page, grouped heads on both sides
+    "A": lambda: fuginex_config([fuginex_parallel(), fuginex_attention(),
+                                 fuginex_attention(weights_of=1), fuginex_parallel(weights_of=0)]),
+    # values of 1 and absent options: one head everywhere, no window, no rotation, no feed-forward, two taps,
+    # constants of 1, low-rank sizes left to the tensors
+    "B": lambda: fuginex_config([fuginex_parallel(heads=1, kv_heads=1, dim=8, window=None, rot_dims=0, r_heads=1, r_kv_heads=1,
+                                                  r_dim=8, r_vdim=8, conv=2, ranks=None, left_scale=1.0, right_scale=1.0, ff=None),
+                                 fuginex_attention(heads=1, kv_heads=1, dim=8, vdim=8, ff=None)], vocab=50, width=24),
+    # widths that are no multiple of 8 (bfloat16 rows off the 16-byte borders), a rotation of the whole head without
+    # scaling, a window of one page and one key, no filter, odd low-rank sizes
+    "C": lambda: fuginex_config([fuginex_parallel(heads=3, kv_heads=1, dim=12, scale=0.2, window=65, rot_dims=12, scaling=None,
+                                                  r_heads=3, r_kv_heads=3, r_dim=10, r_vdim=6, conv=1, ranks=(5, 3), ff=28),
+                                 fuginex_attention(heads=3, kv_heads=3, dim=10, vdim=12, ff=28)] * 2, vocab=33, width=20, eps=1e-6),
+    # head sizes the tensor-core attention has (64 and 128), keys of 128 and values of 64 in the recurrence
+    "T": lambda: fuginex_config([fuginex_parallel(heads=4, kv_heads=2, dim=64, scale=0.12, window=100, rot_dims=32,
+                                                  scaling=(8.0, 128, 16.0, 2.0), r_heads=2, r_kv_heads=1, r_dim=128, r_vdim=64,
+                                                  conv=4, ranks=(16, 24), ff=96),
+                                 fuginex_attention(heads=4, kv_heads=1, dim=128, vdim=128, scale=0.09, ff=96),
+                                 fuginex_parallel(weights_of=0)], vocab=211, width=64),
+}
+
+
+def fuginex_random_config(seed: int) -> dict:
+    """A Fuginex configuration drawn from sizes a model of the design may have: one to four layers of both kinds in any
+    order, some run again with another's tensors, grouped and ungrouped heads, windows below, at and above a page,
+    rotation of none, part or all of a head with or without scaling, filters of 1 to 4 taps, layers without
+    feed-forward."""
+    import random
+    r = random.Random(seed)
+
+    def layer():
+        if r.random() < 0.4:
+            kv = r.choice([1, 2]); dim = r.choice([32, 64, 96, 128])
+            return fuginex_attention(heads=kv * r.choice([1, 2, 4]), kv_heads=kv, dim=dim, vdim=r.choice([dim, 32, 64, 80]),
+                                     scale=r.choice([dim ** -0.5, 0.1]), ff=r.choice([None, 64, 160]))
+        kv = r.choice([1, 2, 4]); dim = r.choice([32, 48, 64, 128]); rkv = r.choice([1, 2, 4])
+        rot = r.choice([0, dim // 2, dim, 16])
+        return fuginex_parallel(heads=kv * r.choice([1, 2, 4]), kv_heads=kv, dim=dim, scale=r.choice([dim ** -0.5, 0.1, 0.2]),
+                                window=r.choice([None, 7, 64, 70, 129, 200]), rot_dims=rot, rot_base=r.choice([1e4, 4e5, 1e6]),
+                                scaling=r.choice([None, (2.0, 1024, 16.0, 1.0), (8.0, 64, 4.0, 0.5), (16.0, 256, 8.0, 2.0)]) if rot else None,
+                                r_heads=rkv * r.choice([1, 2]), r_kv_heads=rkv, r_dim=r.choice([16, 32, 40, 64, 128]),
+                                r_vdim=r.choice([16, 24, 32, 64, 128]), conv=r.choice([1, 2, 3, 4]),
+                                ranks=r.choice([None, (8, 8), (24, 16), (12, 40)]), left_scale=r.choice([1.0, 1.2, 0.4]),
+                                right_scale=r.choice([1.0, 1.1, 0.7]), ff=r.choice([None, 64, 160, 256]))
+    layers = [layer() for _ in range(r.choice([1, 2, 3]))]
+    for _ in range(r.choice([0, 1, 2])):
+        layers.insert(r.randrange(1, len(layers) + 1), dict(weights_of=None))      # filled in below
+    own = [i for i, L in enumerate(layers) if "type" in L]
+    for i, L in enumerate(layers):
+        if "type" not in L:
+            L["weights_of"] = r.choice(own)
+    return fuginex_config(layers, vocab=r.choice([128, 500, 1000]), width=r.choice([64, 96, 128, 256]),
+                          eps=r.choice([1e-5, 1e-6]))
+
+
+def make_fuginex_dir(cfg: dict, out_dir: str, seed: int = 1, dtype=torch.bfloat16, std: float = 0.15, edit=None) -> str:
+    """A Fuginex model folder with seeded random weights; ``edit(name, tensor) -> tensor`` may change them."""
+    from idempotent_llm_b200.config import FuginexConfig
+    from idempotent_llm_b200.weights import write_random_model, write_safetensors, SafetensorsFile
+    write_random_model(FuginexConfig.from_dict(cfg), out_dir, seed=seed, dtype=dtype, std=std)
+    if edit is not None:
+        path = os.path.join(out_dir, "model.safetensors")
+        f = SafetensorsFile(path)
+        tensors = [(n, edit(n, f.get(n).clone())) for n in f.names()]
+        del f
+        write_safetensors(path, tensors)
+    return out_dir
