@@ -124,6 +124,26 @@ def kv_bytes_per_token(eng) -> int:
                for g_ in eng.cache.groups)
 
 
+def cache_bytes_read(lm, lens) -> float:
+    """Bytes of keys and values a single-token step reads for sequences that hold ``lens`` tokens: every cache entry's
+    rows of the keys its layer sees (all, or the last `window`)."""
+    import math
+    eng, total = lm.engine, 0.0
+    windows = {}
+    for e in lm.model.spec.schedule:
+        m = lm.model.spec.layers[e.layer].mixer
+        for b in getattr(m, "branches", None) or [type("B", (), {"mixer": m})]:
+            w = getattr(b.mixer, "window", None)
+            if w:
+                windows[e.cache] = int(w)
+    for g_ in eng.cache.groups:
+        row = (math.prod(g_.need.key_row()) + math.prod(g_.need.value_row())) * g_.k.element_size()
+        for entry in g_.entries:
+            w = windows.get(entry)
+            total += row * sum(min(n, w) if w else n for n in lens)
+    return total
+
+
 def state_bytes_per_sequence(eng) -> int:
     """Per-sequence state of fixed size (a recurrent mixer's), which a decode step reads and writes."""
     return sum(st[0].numel() * st.element_size() for st in eng.cache.state.values())
@@ -161,7 +181,9 @@ def decode_point(lm, lens, steps: int, warmup: int, seed: int, repeats: int = 1,
     ms = statistics.median(times)
     sess.finish()
     mean_len = sum(l + warmup + repeats * steps / 2 for l in lens)
-    bytes_step = step_weight_bytes(lm, batch) + kv_bytes_per_token(eng) * mean_len + 2 * batch * state_bytes_per_sequence(eng)
+    kv_read = (cache_bytes_read(lm, [l + warmup + repeats * steps / 2 for l in lens]) if getattr(cfg, "architecture", "") == "Fuginex"
+               else kv_bytes_per_token(eng) * mean_len)
+    bytes_step = step_weight_bytes(lm, batch) + kv_read + 2 * batch * state_bytes_per_sequence(eng)
     toks = sess.tokens()
     assert toks.shape == (total, batch) and int(toks.min()) >= 0 and int(toks.max()) < V
     for s in slots:
@@ -219,6 +241,35 @@ def lunulix_prefill_flops(cfg, lens) -> float:
     return total + 2 * W * cfg.vocab * len(lens)
 
 
+def fuginex_prefill_flops(cfg, lens) -> float:
+    """The same count for a Fuginex configuration, per layer run: the input and output projections of the layer's
+    mixer (both sides of a parallel layer, with the low-rank pairs), the feed-forward, attention over the keys a query
+    sees (a window bounds them), and the delta rule (per token, head, key channel and value column: decay, the
+    correction's sum, the write and the read-out)."""
+    W, tokens, total = cfg.width, sum(lens), 0.0
+
+    def seen(t, window):                         # keys seen by the queries of a prompt of t tokens
+        if window is None or window >= t:
+            return t * (t + 1) // 2
+        return window * (window + 1) // 2 + (t - window) * window
+    for L in cfg.layers:
+        linear = 3 * W * L.ff if L.ff else 0
+        if L.type == "attention":
+            a = L.attention
+            linear += W * (a.heads * a.dim + a.kv_heads * (a.dim + a.vdim) + a.heads) + a.heads * a.vdim * W
+            total += sum(a.heads * 2 * (a.dim + a.vdim) * seen(t, None) for t in lens)
+        else:
+            l, r = L.left, L.right
+            ra, rg = r.decay_rank or r.dim // 2, r.gate_rank or r.dim // 2
+            linear += W * (l.heads * l.dim + l.kv_heads * l.dim) + l.heads * l.vdim * W
+            linear += W * (2 * r.kv_heads * r.dim + r.heads * r.vdim + r.heads + ra + rg)
+            linear += ra * r.heads * r.dim + rg * r.heads * r.vdim + r.heads * r.vdim * W
+            total += sum(l.heads * 2 * (l.dim + l.vdim) * seen(t, l.window) for t in lens)
+            total += 8 * tokens * r.heads * r.dim * r.vdim
+        total += 2 * tokens * linear
+    return total + 2 * W * cfg.vocab * len(lens)
+
+
 def panodra_prefill_flops(cfg, lens) -> float:
     """The same count for a Panodra configuration, per layer run: the joint input projection, every head's keys and
     values from the latent, the output projection, causal attention per head over keys of dim + rot_dim and values of
@@ -258,6 +309,8 @@ def prefill_flops(cfg, lens) -> float:
     attention, and the head at each prompt's last position."""
     if getattr(cfg, "architecture", "") == "Panodra":
         return panodra_prefill_flops(cfg, lens)
+    if getattr(cfg, "architecture", "") == "Fuginex":
+        return fuginex_prefill_flops(cfg, lens)
     if hasattr(cfg, "layers") and not hasattr(cfg, "hidden_size"):
         return lunulix_prefill_flops(cfg, lens)
     H, L, V = cfg.hidden_size, cfg.num_hidden_layers, cfg.vocab_size
@@ -425,7 +478,8 @@ def decode_kernel_times(lm, lens, seed: int):
     names = ["embed", "embed_scaled", "add_rmsnorm", "post_pre_norm", "rope_table", "gemm_store", "gemm_residual", "gemm_swiglu",
              "gemm_gated", "gemm_qkv", "attention_tc", "attention_generic", "attention_sink", "conv_qkv_cache", "short_conv",
              "ssd_scan", "ssd_group_norm", "token_gate", "gated_act", "attention_lse_gate", "add_dyt", "latent_kv_finish",
-             "headwise", "latent_attention", "experts_few", "act_cast", "concat_cast", "logit_cap"]
+             "headwise", "latent_attention", "experts_few", "act_cast", "concat_cast", "logit_cap", "add_rmsnorm2", "head_finish",
+             "attention_biased", "cols_cast", "delta_prep", "delta_scan", "delta_out", "gate_scale"]
     names = [n for n in names if hasattr(K, n)]
     out, saved = {}, {n: getattr(K, n) for n in names}
     timing = [False]
@@ -461,9 +515,10 @@ def decode_kernel_times(lm, lens, seed: int):
 
 
 def design_comparison(args) -> int:
-    """``--design lunulix`` / ``--design panodra``: decode and prefill throughput of that design beside Qwen3 at equal
-    width, depth (layer runs), heads, feed-forward size and vocabulary (random weights), with where a step's time goes
-    kernel by kernel."""
+    """``--design lunulix`` / ``--design panodra`` / ``--design fuginex``: decode and prefill throughput of that design
+    beside the closest other one (Qwen3; for Fuginex, Lunulix: an attention and a recurrence side by side) at equal width,
+    depth (layer runs), heads, feed-forward size and vocabulary (random weights), with where a step's time goes kernel by
+    kernel."""
     import torch
     import idempotent_llm_b200 as idm
     from idempotent_llm_b200.config.presets import preset
@@ -475,7 +530,7 @@ def design_comparison(args) -> int:
     sampler = ClockSampler()
     sampler.start()
     for size in sizes:
-        for arch in ("qwen3", args.design):
+        for arch in ({"fuginex": "lunulix"}.get(args.design, "qwen3"), args.design):
             cfg = preset(f"{arch}-{size}")
             lm = idm.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=64 * 2304, max_seqs=64, max_seq_len=2304)
             r = {"params_b": lm.model.weight_bytes() / 2e9}
@@ -492,7 +547,8 @@ def design_comparison(args) -> int:
             rows[f"{arch}-{size}"] = r
             del lm
             torch.cuda.empty_cache()
-    print(json.dumps({"metric": f"decode and prefill of {args.design} beside qwen3 at equal sizes (bf16, random weights)",
+    beside = {"fuginex": "lunulix"}.get(args.design, "qwen3")
+    print(json.dumps({"metric": f"decode and prefill of {args.design} beside {beside} at equal sizes (bf16, random weights)",
                       "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3), "dtype": "bf16",
                       "data": "synthetic: seeded random weights and uniform-random token ids", "peaks": pk,
                       "clocks": sampler.stop(), "rows": rows}))
@@ -521,7 +577,7 @@ def main() -> int:
     ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps; the median counts")
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64 and the 32-bit check")
     ap.add_argument("--skip-sizes", action="store_true", help="leave out the points at 8B and 32B layer sizes")
-    ap.add_argument("--design", default="", choices=["", "lunulix", "panodra"],
+    ap.add_argument("--design", default="", choices=["", "lunulix", "panodra", "fuginex"],
                     help="instead of the default workload: this design beside qwen3 at equal layer sizes")
     ap.add_argument("--design-sizes", default="0.6b,8b", help="layer sizes of --design (presets <design>-<size>)")
     args = ap.parse_args()

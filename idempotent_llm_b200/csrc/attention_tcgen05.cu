@@ -72,6 +72,8 @@ struct AttnTcArgs {
     T* out;
     const float* sink;                                 // [n_q] or null: a learned score per head (natural units, not scaled) that joins
                                                        // the softmax's sum with no key and no value
+    const float* slopes;                               // [n_q] or null: slopes[head] * (p - j) is taken off the scaled score of key j
+    int window;                                        // > 0: a query at p sees keys p - window + 1 .. p; 0: every earlier key
     const int* tile_seq; const int* tile_start;
     const int* cu_q; const int* q_start; const int* kv_len; const int* slots;
     const int* table; int table_stride;
@@ -312,15 +314,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int kv_len = a.kv_len[seq];
     const int nb_tile = p_last / AP_BN + 1;                      // the tile's key blocks 0 .. nb_tile-1
     const int R = a.run_blocks;
-    const int n_runs = (nb_tile + R - 1) / R;
+    // With a window, the runs that lie wholly before the first key the tile's first row sees are left out: runs keep
+    // their absolute places, and from here on they are counted from the first one that is walked.
+    const int W = a.window;
+    const int run_lo = W > 0 ? (max(0, p_first - W + 1) / AP_BN) / R : 0;
+    const int n_runs = (nb_tile + R - 1) / R - run_lo;
     if (through_scratch && run >= n_runs) return;                // (the whole block, before anything is set up)
     const int pool_at = parted ? a.tile_pool[tile] : -1;
     const int n_parts = pool_at >= 0 ? (n_runs + a.runs_per_part - 1) / a.runs_per_part : 1;
     if (part >= n_parts) return;
     const bool shared = n_parts > 1;                             // this tile's runs go through the pool, several blocks walk them
     // this block's key blocks b_first .. b_first + nb - 1
-    const int b_first = through_scratch ? run * R : shared ? part * a.runs_per_part * R : 0;
-    const int nb = through_scratch ? min(R, nb_tile - b_first) : shared ? min(a.runs_per_part * R, nb_tile - b_first) : nb_tile;
+    const int b_first = (run_lo + (through_scratch ? run : shared ? part * a.runs_per_part : 0)) * R;
+    const int nb = through_scratch ? min(R, nb_tile - b_first) : shared ? min(a.runs_per_part * R, nb_tile - b_first) : nb_tile - b_first;
     const int n_hg = a.n_q >> gs;
 
     if (threadIdx.x == 0) {
@@ -428,6 +434,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const bool row_live = r < rows_valid;
         const bool warp_live = warp * 32 < rows_valid;           // (a warp without rows keeps the barriers' count and no more)
         const int p_r = p_first + (r >> gs);
+        // the slope in units of the raw score (the scale is positive): raw + slope_raw * (j - p) is what is scaled
+        const float slope_raw = a.slopes ? __fdiv_rn(__fmul_rn(a.slopes[head0 + (r & (gp - 1))], 1.4426950408889634f), a.scale_log2) : 0.f;
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         uint8_t* prow = gbase + S::P_OFF + r * 128;
         if (!row_live) {
@@ -490,6 +498,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     for (int j = 0; j < AP_BN; ++j)
                         if (key0 + j > p_r) sr[j] = 0xff800000u;  // -inf: p becomes 0 exactly
                 }
+                if (W > 0 && key0 + W <= p_r) {                   // some key of the block lies before the row's window
+#pragma unroll
+                    for (int j = 0; j < AP_BN; ++j)
+                        if (key0 + j + W <= p_r) sr[j] = 0xff800000u;
+                }
+                if (a.slopes) {
+                    const float d0 = (float)(key0 - p_r);
+#pragma unroll
+                    for (int j = 0; j < AP_BN; ++j)
+                        sr[j] = __float_as_uint(__fmaf_rn(slope_raw, d0 + (float)j, __uint_as_float(sr[j])));
+                }
                 // the maximum of the raw scores (the scale is positive), four chains side by side
                 // (the three-input maximum of sm_100: two scores per instruction)
                 float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -529,13 +548,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (run_start && shared) {
                     // the run before this block is complete: its result goes to its slot (the MMA that starts the
                     // new run's context overwrites O only after this warp's arrival below)
-                    if (warp_live) leave_run((b_first + b) / R - 1, m_prev, l_prev);
+                    if (warp_live) leave_run((b_first + b) / R - 1 - run_lo, m_prev, l_prev);
                 } else if (run_start) {
                     // the run before this block is complete: fold it into the row's context so far (the MMA
                     // that starts the new run's context overwrites O only after this warp's arrival below)
                     if (warp_live) {
                         float a_, b_;
-                        const bool first = (b_first + b) == R;     // it was the tile's first run: nothing to add to
+                        const bool first = (b_first + b) == (run_lo + 1) * R;   // it was the tile's first run: nothing to add to
                         fold_coeffs(M_tot, L_tot, m_prev, l_prev, a_, b_);
                         float4* mine = reinterpret_cast<float4*>(tot);
 #pragma unroll 1
@@ -611,7 +630,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // nobody waits for anybody for ever.)
             if (ok && warp_live) {
                 tc_fence_after();
-                leave_run(through_scratch ? run : (b_first + nb - 1) / R, m_ref, l);
+                leave_run(through_scratch ? run : (b_first + nb - 1) / R - run_lo, m_ref, l);
                 __threadfence();
             }
             count_and_fold_runs<HD>(a, part0, part_floats, n_runs, through_scratch ? n_runs : n_parts, rows_valid, tok0, head0,
@@ -699,7 +718,7 @@ extern "C" long long idm_attention_tc_scratch_floats(int n_tiles, int n_q, int n
 // 128 / heads_per_tile tokens, longest first; rows_cap: the most rows (tokens x heads_per_tile) any tile has.  max_runs > 0: every run of `run_blocks` key blocks is a
 // block of its own and results meet in scratch; max_runs == 0:
 // one block per tile and head group (`scratch` may be null if no tile has more than run_blocks key blocks).
-static int attention_tc_any(const void* q, void* out, const float* sink, const void* k_pool, const void* v_pool, int n_pages,
+static int attention_tc_any(const void* q, void* out, const float* sink, const float* slopes, int window, const void* k_pool, const void* v_pool, int n_pages,
                             const int* table, int table_stride, const int* tile_seq, const int* tile_start,
                             int n_tiles, const int* cu_q, const int* q_start, const int* kv_len,
                             const int* slots, int n_tokens, int n_q, int n_kv, int hd, float scale,
@@ -739,7 +758,7 @@ static int attention_tc_any(const void* q, void* out, const float* sink, const v
         IDM_REQUIRE(r == 0, "attention_tc: tensor map for v failed (%d)", r);
     }
     AttnTcArgs a;
-    a.out = (T*)out; a.sink = sink; a.tile_seq = tile_seq; a.tile_start = tile_start; a.cu_q = cu_q; a.q_start = q_start;
+    a.out = (T*)out; a.sink = sink; a.slopes = slopes; a.window = window > 0 ? window : 0; a.tile_seq = tile_seq; a.tile_start = tile_start; a.cu_q = cu_q; a.q_start = q_start;
     a.kv_len = kv_len; a.slots = slots; a.table = table; a.table_stride = table_stride;
     a.n_q = n_q; a.n_kv = n_kv; a.gp_shift = gs; a.scale_log2 = scale * 1.4426950408889634f;
     a.run_blocks = run_blocks; a.max_runs = max_runs; a.rows_cap = rows_cap;
@@ -748,7 +767,8 @@ static int attention_tc_any(const void* q, void* out, const float* sink, const v
     a.pool = a.parts ? a.parts + groups * (long long)(AP_BM * hd) : nullptr;
     IDM_REQUIRE(a.max_parts == 0 || (scratch != nullptr && runs_per_part >= 1 && groups <= AP_COUNTERS),
                 "attention_tc: shared tiles need scratch, runs_per_part >= 1 and at most %d tiles x head groups (got %lld)", AP_COUNTERS, groups);
-    if (g_attn_few_rows && attention_few_rows_can(hd, rows_cap, run_blocks, max_runs, groups))
+    // (the kernel for few rows has neither windows nor slopes: such layers' single tokens take the general one, a block a run)
+    if (g_attn_few_rows && slopes == nullptr && window <= 0 && attention_few_rows_can(hd, rows_cap, run_blocks, max_runs, groups))
         return hd == 64 ? launch_attention_few_rows<64>(mk, mv, a, (const T*)q, n_tiles, stream)
                         : launch_attention_few_rows<128>(mk, mv, a, (const T*)q, n_tiles, stream);
     return hd == 64 ? launch_attention_tc<64>(mq, mk, mv, a, n_tiles, stream)
@@ -761,7 +781,7 @@ extern "C" int idm_attention_tc(const void* q, void* out, const void* k_pool, co
                                 const int* slots, int n_tokens, int n_q, int n_kv, int hd, float scale,
                                 int run_blocks, int max_runs, int rows_cap, float* scratch, const int* tile_pool,
                                 int max_parts, int runs_per_part, cudaStream_t stream) {
-    return attention_tc_any(q, out, nullptr, k_pool, v_pool, n_pages, table, table_stride, tile_seq, tile_start, n_tiles, cu_q,
+    return attention_tc_any(q, out, nullptr, nullptr, 0, k_pool, v_pool, n_pages, table, table_stride, tile_seq, tile_start, n_tiles, cu_q,
                             q_start, kv_len, slots, n_tokens, n_q, n_kv, hd, scale, run_blocks, max_runs, rows_cap, scratch,
                             tile_pool, max_parts, runs_per_part, stream);
 }
@@ -774,9 +794,25 @@ extern "C" int idm_attention_tc_sink(const void* q, void* out, const float* sink
                                      const int* kv_len, const int* slots, int n_tokens, int n_q, int n_kv, int hd,
                                      float scale, int run_blocks, int max_runs, int rows_cap, float* scratch,
                                      const int* tile_pool, int max_parts, int runs_per_part, cudaStream_t stream) {
-    return attention_tc_any(q, out, sink, k_pool, v_pool, n_pages, table, table_stride, tile_seq, tile_start, n_tiles, cu_q,
+    return attention_tc_any(q, out, sink, nullptr, 0, k_pool, v_pool, n_pages, table, table_stride, tile_seq, tile_start, n_tiles, cu_q,
                             q_start, kv_len, slots, n_tokens, n_q, n_kv, hd, scale, run_blocks, max_runs, rows_cap, scratch,
                             tile_pool, max_parts, runs_per_part, stream);
+}
+
+// The same attention with every option: a sink per q-head (or null), a slope per q-head (or null: slopes[head] times
+// the distance to a key is taken off its scaled score), a window (> 0: a query sees itself and the window - 1 keys
+// before it; the cache keeps every key, runs of key blocks that no row of a tile sees are not walked).
+extern "C" int idm_attention_tc_biased(const void* q, void* out, const float* sink, const float* slopes, int window,
+                                       const void* k_pool, const void* v_pool, int n_pages, const int* table,
+                                       int table_stride, const int* tile_seq, const int* tile_start, int n_tiles,
+                                       const int* cu_q, const int* q_start, const int* kv_len, const int* slots,
+                                       int n_tokens, int n_q, int n_kv, int hd, float scale, int run_blocks, int max_runs,
+                                       int rows_cap, float* scratch, const int* tile_pool, int max_parts,
+                                       int runs_per_part, cudaStream_t stream) {
+    IDM_REQUIRE(scale > 0.f, "attention_tc: the scale of the scores must be positive, not %g", (double)scale);
+    return attention_tc_any(q, out, sink, slopes, window, k_pool, v_pool, n_pages, table, table_stride, tile_seq, tile_start,
+                            n_tiles, cu_q, q_start, kv_len, slots, n_tokens, n_q, n_kv, hd, scale, run_blocks, max_runs,
+                            rows_cap, scratch, tile_pool, max_parts, runs_per_part, stream);
 }
 
 // 0: tiles of few rows go through the tcgen05 kernel as well (tests compare the two bit for bit); returns the old setting

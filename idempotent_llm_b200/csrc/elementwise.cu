@@ -600,7 +600,7 @@ extern "C" int idm_token_gate(const float* s, const int* tokens, const void* tab
 // out[t, out_col + c] = o[t, c] * sigmoid(gate[t * gate_stride + c]) * scale   (gate null: only the constant);
 // o [N, width] in the storage type, gate 32-bit (columns of a wider projection), out rows of out_stride.
 __global__ void __launch_bounds__(256) gate_scale_kernel(const T* __restrict__ o, const float* __restrict__ gate,
-                                                         int gate_stride, float scale, T* __restrict__ out,
+                                                         int gate_stride, int gate_group, float scale, T* __restrict__ out,
                                                          int out_stride, int out_col, int width) {
     pdl_launch_dependents();
     pdl_wait();
@@ -613,18 +613,19 @@ __global__ void __launch_bounds__(256) gate_scale_kernel(const T* __restrict__ o
     for (int i = 0; i < 4; ++i) {
         if (c + i >= width) break;
         float v = to_f32(src[i]);
-        if (gate) v = v / (1.0f + expf(-gate[t * gate_stride + c + i]));
+        if (gate) v = v / (1.0f + expf(-gate[t * gate_stride + (c + i) / gate_group]));
         from_f32(dst[i], v * scale);
     }
 }
 
-extern "C" int idm_gate_scale(const void* o, const float* gate, int gate_stride, float scale, void* out,
+extern "C" int idm_gate_scale(const void* o, const float* gate, int gate_stride, int gate_group, float scale, void* out,
                               int out_stride, int out_col, int n_tokens, int width, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     IDM_REQUIRE(width > 0 && out_col >= 0 && out_col + width <= out_stride, "gate_scale: columns %d..%d of rows of %d", out_col,
                 out_col + width, out_stride);
+    IDM_REQUIRE(gate_group >= 1, "gate_scale: a gate serves %d columns", gate_group);
     idm_launch(gate_scale_kernel, dim3(n_tokens, (width + 1023) / 1024), dim3(256), 0, stream, (const T*)o, gate, gate_stride,
-               scale, (T*)out, out_stride, out_col, width);
+               gate_group, scale, (T*)out, out_stride, out_col, width);
     IDM_LAUNCH_CHECK("gate_scale");
     return 0;
 }

@@ -96,7 +96,8 @@ SIGNATURES = {
     "idm_attention_tc_scratch_floats": (c_longlong, "iiiiii"),
     "idm_attention_tc": (c_int, "ppppipippippppiiiifiiippiip"),
     "idm_attention_tc_sink": (c_int, "pppppipippippppiiiifiiippiip"),
-    "idm_gate_scale": (c_int, "ppifpiiiip"),
+    "idm_attention_tc_biased": (c_int, "ppppippipippippppiiiifiiippiip"),
+    "idm_gate_scale": (c_int, "ppiifpiiiip"),
     "idm_attention_tc_status": (c_int, ""),
     "idm_attention_tc_set_few_rows": (c_int, "i"),
     "idm_latent_kv_finish": (c_int, "piiiiipfpifppippppip"),
@@ -587,7 +588,8 @@ class Kernels:
             return self.attention_tc(q, kv, ctx, scale)
         return self.attention_generic(q, kv, ctx, k_new, v_new, scale, window)
 
-    def attention_tc(self, q, kv, ctx, scale: float, out=None, through_scratch=None, share=None, sink=None) -> torch.Tensor:
+    def attention_tc(self, q, kv, ctx, scale: float, out=None, through_scratch=None, share=None, sink=None, slopes=None,
+                     window=None) -> torch.Tensor:
         """Causal attention on the tensor cores: tiles of (128 / gp tokens) x (gp q-heads of one kv-head).
 
         Steps with few tokens per sequence (at most 32 rows a tile: single tokens above all) give every
@@ -605,7 +607,14 @@ class Kernels:
                 _p(ctx.kv_len), _p(ctx.slots), n, n_q, kv.n_kv_heads,
                 hd, scale, self.attention_run_blocks, max_runs, rows_cap, scratch, tile_pool, max_parts, per,
                 self._stream())
-        if sink is None:
+        if slopes is not None or window:
+            # a slope per q-head times the distance to a key off its score, and a window of keys a query sees (runs of
+            # key blocks before every window of a tile are not walked)
+            for name, t in (("sink", sink), ("slopes", slopes)):
+                if t is not None and (t.dtype != torch.float32 or t.numel() != n_q):
+                    raise KernelError(f"attention: {name} must hold one 32-bit number per head")
+            self._check(self.lib.idm_attention_tc_biased(_p(q), _p(out), _p(sink), _p(slopes), int(window) if window else 0, *rest))
+        elif sink is None:
             self._check(self.lib.idm_attention_tc(_p(q), _p(out), *rest))
         else:
             # a learned score per q-head that joins the softmax's sum with no key and no value
@@ -621,13 +630,14 @@ class Kernels:
         return (self.dtype == torch.bfloat16 and self.attention_impl == "tcgen05" and hd == dv and kv.ring == 0
                 and bool(self.lib.idm_attention_tc_supports(hd)))
 
-    def gate_scale(self, o, gate, gate_stride: int, scale: float, out, out_col: int) -> None:
+    def gate_scale(self, o, gate, gate_stride: int, scale: float, out, out_col: int, gate_group: int = 1) -> None:
         """``out[:, out_col : out_col + width] = o * sigmoid(gate) * scale`` (``gate``: a 32-bit view with row stride
-        ``gate_stride``, or None for the constant alone)."""
+        ``gate_stride``, or None for the constant alone; ``gate_group`` columns in a row share one gate number: a head's
+        size for a gate per head)."""
         self._need(o, self.dtype, "mixer output")
         self._need(out, self.dtype, "gated output")
         n, width = o.shape
-        self._check(self.lib.idm_gate_scale(_p(o), (gate.data_ptr() if gate is not None else None), gate_stride,
+        self._check(self.lib.idm_gate_scale(_p(o), (gate.data_ptr() if gate is not None else None), gate_stride, int(gate_group),
                                             float(scale), _p(out), out.shape[1], out_col, n, width, self._stream()))
 
     def attention_tc_plan(self, ctx, n_q: int, n_kv: int, hd: int, through_scratch=None, share=None):

@@ -143,6 +143,64 @@ def test_normed_attention_alone_prompt_then_single_tokens(dtype, variant):
     assert helpers.rel_err(torch.cat(outs), ref) < TOL[dtype]
 
 
+TC_SHAPES = {
+    # (head size, q-heads, kv-heads, window, slopes): tiles of 16, 64 and 128 tokens; windows below a page, across many
+    # runs of key blocks, and wider than the sequence
+    "w600_h64_g8": (64, 8, 1, 600, False),
+    "w1100_h128_g2": (128, 4, 2, 1100, False),
+    "slopes_h128_g1": (128, 2, 2, None, True),
+    "w65_slopes_h64_g4": (64, 4, 1, 65, True),
+    "w9000_h64_g2": (64, 2, 1, 9000, False),
+    "w1_h64_g1": (64, 1, 1, 1, False),
+}
+
+
+@pytest.mark.parametrize("shape", sorted(TC_SHAPES))
+def test_windows_and_slopes_on_the_tensor_cores_against_the_general_kernel(shape):
+    """bfloat16 with head sizes of 64 and 128 runs on the tensor cores; the general kernel is the witness.  Two unequal
+    sequences in the same steps: a long prompt (tiles shared by several blocks, runs of key blocks before the window
+    left out), a portion, single tokens (a block per run), with and without the kernel's other ways through scratch."""
+    hd, H, G, window, slopes = TC_SHAPES[shape]
+    spec = _head_spec(hidden=32, n_heads=H, n_kv_heads=G, key_dim=hd, value_dim=hd, softmax_scale=hd ** -0.5, window=window,
+                      unit_sink=window is not None, slope_exponent=6.0 if slopes else None, head_gate=slopes)
+    cls = MIXERS.get(spec.kind)
+    w = random_weights(cls.declare(spec, "M."), 9, 0.3, dtype=torch.bfloat16, device="cuda")
+    w["M.q.norm"] = (w["M.q.norm"].float() * 2.5).to(torch.bfloat16)       # sharp scores: single keys carry weight
+    lens = (2900, 1500)
+    x = [(torch.randn(n, 32, generator=torch.Generator().manual_seed(3 + n)) * 1.5).to(torch.bfloat16).cuda() for n in lens]
+    outs = {}
+    for impl, scratch in (("generic", None), ("tcgen05", None), ("tcgen05", True), ("tcgen05", False)):
+        rt = _rt("bfloat16")
+        rt.kernels.attention_impl = impl
+        if scratch is not None:                          # every run a block of its own / no tile shared
+            plan = rt.kernels.attention_tc_plan
+            rt.kernels.attention_tc_plan = (lambda *a, _p=plan, **k: _p(*a[:4], through_scratch=True)) if scratch else \
+                (lambda *a, _p=plan, **k: _p(*a[:4], share=False))
+        calls, inner = [], rt.kernels.attention_tc
+        rt.kernels.attention_tc = lambda *a, _f=inner, **k: (calls.append(1), _f(*a, **k))[1]
+        part = cls(spec, w, "M.", rt)
+        cache = SequenceCache({0: cls.cache_need(spec)}, 64 * 80, torch.bfloat16, "cuda:0", max_seqs=2)
+        slots = [cache.alloc_slot(), cache.alloc_slot()]
+        got, at = [[], []], [0, 0]
+        steps = [(2500, 1200), (380, 290)] + [(1, 1)] * 10 + [(10, 0)]
+        for step in steps:
+            live = [i for i in (0, 1) if step[i]]
+            hi = [at[i] + step[i] for i in live]
+            cache.reserve([(slots[i], h) for i, h in zip(live, hi)]); cache.flush()
+            ctx = _ctx([slots[i] for i in live], [at[i] for i in live], [step[i] for i in live])
+            y = part.forward(torch.cat([x[i][at[i]:h] for i, h in zip(live, hi)]), ctx, cache.view(0), None, True).sum(0)
+            off = 0
+            for i, h in zip(live, hi):
+                got[i].append(y[off:off + step[i]]); off += step[i]
+                cache.set_length(slots[i], h); at[i] = h
+        assert rt.kernels.attention_tc_status() == 0 and (len(calls) == len(steps)) == (impl == "tcgen05")
+        outs[(impl, scratch)] = [torch.cat(g) for g in got]
+    want = outs[("generic", None)]
+    for key, got in outs.items():
+        for i in (0, 1):
+            assert helpers.rel_err(got[i], want[i]) < 2e-2, f"{key}, sequence {i}"
+
+
 def test_the_unit_sink_takes_weight_without_a_value():
     """Scores far below 0 leave the weight with the sink and the output at the output bias; scores far above 0 make it
     ordinary softmax attention."""
