@@ -310,7 +310,7 @@ def main(argv=None) -> int:
 
     k = sub.add_parser("kernel-bench", help="one kernel alone at a preset's layer sizes")
     k.add_argument("--kernel", required=True, choices=["attention_single", "attention_single_mma", "attention_prompt", "gemm", "gemm_fused", "step_trace",
-                            "ssd_mixer", "latent_mixer"])
+                            "ssd_mixer", "latent_mixer", "delta_mixer"])
     k.add_argument("--size", default="qwen3-0.6b")
     k.add_argument("--batch", type=int, default=8)
     k.add_argument("--context", type=int, default=3000)

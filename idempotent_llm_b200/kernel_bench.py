@@ -18,6 +18,8 @@ def run(args) -> int:
         return ssd_mixer(args, cfg)
     if args.kernel == "latent_mixer":
         return latent_mixer(args, cfg)
+    if args.kernel == "delta_mixer":
+        return delta_mixer(args, cfg)
     K = Kernels(torch.bfloat16, "cuda:0")
     # which kernel a product of many tokens takes (defaults: what the library chooses by itself)
     K.gemm_choices(pair=None if getattr(args, "pairs", None) is None else bool(args.pairs),
@@ -146,6 +148,50 @@ def ssd_mixer(args, cfg) -> int:
         torch.cuda.synchronize()
         if i >= 3:
             print(f"ssd mixer, {B} x {T} tokens: {e0.elapsed_time(e1) * 1e3:.1f} us")
+    return 0
+
+
+def delta_mixer(args, cfg) -> int:
+    """The gated delta rule of a preset's first parallel layer alone (``--size fuginex-0.6b``) on ``--batch`` prompts
+    of ``--context`` tokens: the whole mixer, then the recurrence by itself on unit keys and random decays, with the
+    32-bit multiply-adds it has to do (four per state element and token)."""
+    from .cache import SequenceCache
+    from .engine.batch import context_from_packed, pack_step_host
+    from .kernels import Kernels
+    from .parts import MIXERS, Runtime
+    from .weights import random_weights
+    spec = next(b.mixer for L in cfg.to_model_spec().layers if hasattr(L.mixer, "branches")
+                for b in L.mixer.branches if b.mixer.kind == "gated_delta")
+    dev = torch.device("cuda:0")
+    rt = Runtime(device=dev, dtype=torch.bfloat16, kernels=Kernels(torch.bfloat16, dev))
+    cls = MIXERS.get(spec.kind)
+    part = cls(spec, random_weights(cls.declare(spec, "m."), 1, 0.02, dtype=torch.bfloat16, device="cuda"), "m.", rt)
+    B, T = args.batch, args.context
+    cache = SequenceCache({0: cls.cache_need(spec)}, 64 * B, torch.bfloat16, "cuda:0", max_seqs=B)
+    slots = [cache.alloc_slot() for _ in range(B)]
+    x = torch.randn(B * T, spec.hidden, device="cuda").to(torch.bfloat16)
+    packed, n, q_lens = pack_step_host(slots, [0] * B, [[0] * T] * B)
+    ctx = context_from_packed(packed.cuda(), n, slots, q_lens, [0] * B)
+    H, Hk, dk, dv = spec.heads, spec.kv_heads, spec.key_dim, spec.value_dim
+    qk = Hk * dk
+    c = torch.randn(B * T, 2 * qk + H * dv, device="cuda")
+    c[:, :2 * qk] = torch.nn.functional.normalize(c[:, :2 * qk].reshape(B * T, 2 * Hk, dk), dim=-1).reshape(B * T, -1)
+    g = torch.rand(B * T, H * dk, device="cuda") * 0.2 + 0.8
+    beta = torch.rand(B * T, H, device="cuda")
+    state = cache.state_of(0)[:, part.conv_floats:]
+    runs = {"delta mixer": lambda: part.forward(x, ctx, None, cache.state_of(0), True),
+            "recurrence alone": lambda: rt.kernels.delta_scan(c, 0, qk, 2 * qk, g, 0, beta, state, ctx, H, Hk, dk, dv)}
+    for name, fn in runs.items():
+        for i in range(args.reps + 3):
+            ctx.memo.clear()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                print(f"{name}, {B} x {T} tokens: {e0.elapsed_time(e1) * 1e3:.1f} us"
+                      + (f" ({4 * B * T * H * dk * dv / 1e9:.2f} G multiply-adds)" if name != "delta mixer" else ""))
     return 0
 
 

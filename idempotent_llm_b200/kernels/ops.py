@@ -73,7 +73,8 @@ SIGNATURES = {
     "idm_head_finish": (c_int, "piiiipppppfipfiiiippppiipppip"),
     "idm_cols_cast": (c_int, "piiipiip"),
     "idm_delta_prep": (c_int, "piiipiipiipppiiiip"),
-    "idm_delta_scan": (c_int, "piiiipiippqpippiiiiip"),
+    "idm_delta_scan": (c_int, "piiiipiippqpippiiiiiipp"),
+    "idm_delta_scan_scratch_floats": (c_longlong, "iiii"),
     "idm_delta_out": (c_int, "pipfpiifpiiiiip"),
     "idm_add_rmsnorm2": (c_int, "ppiqppfpppiip"),
     "idm_gemm_bf16_gated": (c_int, "pppiiiip"),
@@ -453,9 +454,11 @@ class Kernels:
         returns the read-outs ``[N, H * dv]`` in 32-bit."""
         n = c.shape[0]
         o = torch.empty((n, H * dv), dtype=torch.float32, device=self.device)
+        want = int(self.lib.idm_delta_scan_scratch_floats(n, H, dk, int(ctx.max_q_len)))
+        scratch = torch.empty((want,), dtype=torch.float32, device=self.device) if want else None
         self._check(self.lib.idm_delta_scan(_p(c), c.shape[1], c_q, c_k, c_v, _p(g), g.shape[1], g_col, _p(beta), _p(state),
                                             self._state_stride(state), _p(o), H * dv, _p(ctx.cu_q), _p(ctx.slots),
-                                            ctx.n_seqs, H, Hk, dk, dv, self._stream()))
+                                            ctx.n_seqs, H, Hk, dk, dv, int(ctx.max_q_len), _p(scratch), self._stream()))
         return o
 
     def delta_out(self, o, w, eps: float, gate, gate_col: int, scale: float, out, out_col: int, H: int, dv: int) -> None:

@@ -293,6 +293,50 @@ def test_the_delta_rule_overwrites_what_a_key_held():
     assert (y - want).abs().max() < 1e-6 and float(state[0].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("T", [67, 16, 33])
+@pytest.mark.parametrize("dk,dv,H,Hk", [(4, 3, 1, 1), (10, 20, 2, 1), (32, 16, 2, 2), (64, 40, 4, 2), (128, 64, 2, 1), (136, 8, 1, 1)])
+def test_long_and_short_portions_walk_the_recurrence_to_the_same_numbers(dk, dv, H, Hk, T):
+    """Portions of at most four tokens are walked token by token from global memory; longer ones run sixteen tokens
+    at a time (keys of up to 128: the sums against the state as products, the corrections from a triangular system)
+    or are walked through shared memory (wider keys: the same bits as the short walk).  One portion and portions of
+    at most four give the same read-outs and state, and both agree with the recurrence written out.  Some decays are
+    so strong that their product over a chunk underflows; some are exactly 1."""
+    K = _rt("float32").kernels
+    gen = torch.Generator().manual_seed(dk * 131 + dv)
+    qk = Hk * dk
+    c = torch.randn(T, 2 * qk + H * dv, generator=gen)
+    c[:, :2 * qk] = torch.nn.functional.normalize(c[:, :2 * qk].reshape(T, 2 * Hk, dk), dim=-1).reshape(T, -1)
+    g = torch.rand(T, H * dk, generator=gen) * 0.5 + 0.5
+    g[:, 0] = 1e-6
+    g[:, 1] = 1.0
+    g[T // 2, :] = 1e-4
+    beta = torch.rand(T, H, generator=gen)
+    cd, gd, bd = c.cuda(), g.cuda(), beta.cuda()
+    got = []
+    for sizes in ([T], [4, 3, 1, 2]):
+        state = torch.zeros(2, H * dk * dv, device="cuda")
+        ys = []
+        for lo, hi in _cuts(T, sizes):
+            ys.append(K.delta_scan(cd[lo:hi].contiguous(), 0, qk, 2 * qk, gd[lo:hi].contiguous(), 0, bd[lo:hi].contiguous(),
+                                   state, _ctx([1], [lo], [hi - lo]), H, Hk, dk, dv))
+        got.append((torch.cat(ys).cpu(), state[1].cpu().clone()))
+        assert float(state[0].abs().max()) == 0.0
+    if dk > 128:
+        assert torch.equal(got[0][0], got[1][0]) and torch.equal(got[0][1], got[1][1])
+    assert helpers.rel_err(got[0][0], got[1][0]) < 1e-5 and helpers.rel_err(got[0][1], got[1][1]) < 1e-5
+    S = torch.zeros(H, dk, dv, dtype=torch.float64)
+    want = torch.zeros(T, H, dv, dtype=torch.float64)
+    for t in range(T):
+        for h in range(H):
+            q, k = (c[t, o + (h // (H // Hk)) * dk:][:dk].double() for o in (0, qk))
+            v = c[t, 2 * qk + h * dv:][:dv].double()
+            S[h] = g[t, h * dk:(h + 1) * dk].double()[:, None] * S[h]
+            S[h] = S[h] + torch.outer(k, float(beta[t, h]) * (v - S[h].T @ k))
+            want[t, h] = S[h].T @ q
+    assert helpers.rel_err(got[0][0].reshape(T, H, dv), want) < 1e-5
+    assert helpers.rel_err(got[0][1].reshape(H, dv, dk).transpose(1, 2), S) < 1e-5
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_parallel_mixer_is_the_weighted_sum_of_its_branches(dtype):
     left = HEAD_VARIANTS["windowed"]()
