@@ -117,8 +117,17 @@ __global__ void __launch_bounds__(DS_COLS * 8) delta_scan_kernel(DeltaScanArgs a
     const int t0 = a.cu_q[s], t1 = a.cu_q[s + 1];
     float* sp = a.state + (size_t)a.slots[s] * a.state_stride + ((size_t)h * a.dv + (col ? j : 0)) * a.dk + row0;
     float S[RP], kq[3][RP];                           // (k, q, g of the token at hand)
+    const bool vec = a.dk % 4 == 0 && ((uintptr_t)sp & 15) == 0;      // a thread's rows as 16-byte pieces
 #pragma unroll
-    for (int i = 0; i < RP; ++i) S[i] = (col && row0 + i < a.dk) ? sp[i] : 0.f;
+    for (int i = 0; i < RP; i += 4) {
+        if (vec) {
+            const float4 x = (col && row0 + i < a.dk) ? *reinterpret_cast<const float4*>(sp + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            S[i] = x.x; S[i + 1] = x.y; S[i + 2] = x.z; S[i + 3] = x.w;
+        } else {
+#pragma unroll
+            for (int e = i; e < i + 4; ++e) S[e] = (col && row0 + e < a.dk) ? sp[e] : 0.f;
+        }
+    }
 
     auto load = [&](int t, float (&dst)[3][RP]) {
         const float* kp = a.c + (size_t)t * a.c_stride + a.c_k + hk * a.dk + row0;
@@ -163,8 +172,15 @@ __global__ void __launch_bounds__(DS_COLS * 8) delta_scan_kernel(DeltaScanArgs a
     }
     if (col) {
 #pragma unroll
-        for (int i = 0; i < RP; ++i)
-            if (row0 + i < a.dk) sp[i] = S[i];
+        for (int i = 0; i < RP; i += 4) {
+            if (vec) {
+                if (row0 + i < a.dk) *reinterpret_cast<float4*>(sp + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+            } else {
+#pragma unroll
+                for (int e = i; e < i + 4; ++e)
+                    if (row0 + e < a.dk) sp[e] = S[e];
+            }
+        }
     }
 }
 
@@ -384,21 +400,26 @@ __global__ void __launch_bounds__(128) delta_pairs_kernel(DeltaScanArgs a, float
     }
 }
 
-// The chunk kernel: a block owns (sequence, head, 16 columns of S), a warp one column, lane L rows [L RP, (L + 1) RP)
-// of it.  Per chunk: (1) all threads turn the staged k, q, g in place into k G_C / G_t, q G_t, k G_t, four tokens a
-// thread, with the four groups' products joined through shared memory; (2) the warp lays its column of S0 into shared
-// memory, and lane t sums S0^T (G_t k_t) for token t's correction, lane 16 + t S0^T (G_t q_t) for its read-out; (3) the triangular system runs down the
-// lanes: u_s goes from lane s to all, lane L adds row s's entry L of [-A | B] times u_s to its sum; (4) lanes 16.. store
-// the read-outs, all lanes bring their rows of S behind the chunk.
+// The chunk kernel: a block owns (sequence, head, 16 columns of S), a warp four of the columns, lane L rows
+// [L RP, (L + 1) RP) of each.  Four columns a warp, because what a warp reads from shared memory (a token's scaled k or
+// q) then serves four sums, and four independent chains keep one warp per scheduler busy.  Per chunk: (1) the threads
+// turn the staged k, q, g in place into k G_C / G_t, q G_t, k G_t, a thread per channel and group of tokens, the
+// groups' products joined through shared memory; (2) the warp lays its columns of S0 into shared memory, and lane t
+// sums S0^T (G_t k_t) for token t's correction, lane 16 + t S0^T (G_t q_t) for its read-out; (3) the triangular system
+// runs down the lanes: u_s goes from lane s to all, lane L adds row s's entry L of [-A | B] times u_s to its sum; (4)
+// lanes 16.. store the read-outs, all lanes bring their rows of S behind the chunk.
+#define DC_NC 4                                                 // columns per warp
 template <int RP>
 struct DeltaChunk {
-    static constexpr int DKP = RP * 32;
+    static constexpr int DKP = RP * 32, NT = DS_COLS / DC_NC * 32;
+    static constexpr int NG = NT / DKP < 1 ? 1 : NT / DKP;      // groups of tokens in step (1)
     static constexpr int V_AT = 3 * DKP, BETA_AT = V_AT + DS_COLS, AB_AT = BETA_AT + 4;
     static constexpr int ROW = AB_AT + 2 * DC_C;                // k, q, g, v of the block's columns, beta, -A and B
     static constexpr int GC_AT = 2 * DC_C * ROW;                // the chunk's whole decay, behind the two stages
-    static constexpr int GP_AT = GC_AT + DKP;                   // the four token groups' decays
-    static constexpr int SW_AT = GP_AT + 4 * DKP;               // a column of S per warp
+    static constexpr int GP_AT = GC_AT + DKP;                   // the token groups' decays
+    static constexpr int SW_AT = GP_AT + NG * DKP;              // the block's columns of S
     static constexpr int FLOATS = SW_AT + DS_COLS * DKP;
+    static_assert(DKP <= NT && DC_C % NG == 0, "a thread per channel, whole groups of tokens");
 };
 
 template <int RP>
@@ -409,14 +430,13 @@ __device__ __forceinline__ void load_rows(const float* p, float (&x)[RP]) {
 }
 
 template <int RP, bool VEC>
-__global__ void __launch_bounds__(DS_COLS * 32) delta_scan_chunked_kernel(DeltaScanArgs a, const float* __restrict__ ab) {
+__global__ void __launch_bounds__(DeltaChunk<RP>::NT) delta_scan_chunked_kernel(DeltaScanArgs a, const float* __restrict__ ab) {
     using L = DeltaChunk<RP>;
-    constexpr int C = DC_C, NT = DS_COLS * 32;
+    constexpr int C = DC_C, NT = L::NT, NC = DC_NC, NW = NT / 32;
     extern __shared__ __align__(16) float ds_smem[];
     pdl_launch_dependents();
     const int s = blockIdx.z, h = blockIdx.y, hk = h / (a.H / a.Hk);
-    const int tid = threadIdx.x, lane = tid & 31, jl = tid >> 5, j0 = blockIdx.x * DS_COLS, j = j0 + jl;
-    const bool col = j < a.dv;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, j0 = blockIdx.x * DS_COLS, jw = warp * NC;
     const int row0 = lane * RP;
     for (int e = tid; e < 2 * C * L::DKP; e += NT) {            // channels past dk: k = q = 0, g = 1, never copied
         const int row = e / L::DKP, p = e % L::DKP;
@@ -427,17 +447,19 @@ __global__ void __launch_bounds__(DS_COLS * 32) delta_scan_chunked_kernel(DeltaS
     }
     pdl_wait();
     const int t0 = a.cu_q[s], t1 = a.cu_q[s + 1];
-    float* sp = a.state + (size_t)a.slots[s] * a.state_stride + ((size_t)h * a.dv + (col ? j : 0)) * a.dk + row0;
-    float S[RP];
+    float* sp = a.state + (size_t)a.slots[s] * a.state_stride + ((size_t)h * a.dv + j0 + jw) * a.dk + row0;
+    float S[NC][RP];
 #pragma unroll
-    for (int i = 0; i < RP; ++i) S[i] = (col && row0 + i < a.dk) ? sp[i] : 0.f;
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int i = 0; i < RP; ++i) S[c][i] = (j0 + jw + c < a.dv && row0 + i < a.dk) ? sp[(size_t)c * a.dk + i] : 0.f;
 
     const int cols = min(DS_COLS, a.dv - j0);
-    static_assert(DS_COLS == DC_C, "warp w of a block copies token w of a chunk");
     auto issue = [&](int tb, int stage) {
-        if (jl < min(C, t1 - tb)) {
-            const int t = tb + jl;
-            float* row = ds_smem + (stage * C + jl) * L::ROW;
+        const int n = min(C, t1 - tb);
+        for (int tt = warp; tt < n; tt += NW) {
+            const int t = tb + tt;
+            float* row = ds_smem + (stage * C + tt) * L::ROW;
             const float* kp = a.c + (size_t)t * a.c_stride + hk * a.dk;
             const float* gp = a.g + (size_t)t * a.g_stride + a.g_col + h * a.dk;
             if (VEC) {
@@ -474,93 +496,125 @@ __global__ void __launch_bounds__(DS_COLS * 32) delta_scan_chunked_kernel(DeltaS
             st[(n + e / L::ROW) * L::ROW + c] = (c >= 2 * L::DKP && c < 3 * L::DKP) ? 1.f : 0.f;
         }
         __syncthreads();
-        // (1) in place, per channel: k -> k G_C / G_t, q -> q G_t, g -> k G_t; and G_C.  Thread (channel, group of 4 tokens).
+        // (1) in place, per channel: k -> k G_C / G_t, q -> q G_t, g -> k G_t; and G_C.  Thread (channel, group of tokens).
         {
-            const int p = tid % L::DKP, grp = tid / L::DKP;     // (blocks have at least 4 DKP threads)
-            float g4[4], k4[4], q4[4];
-            if (grp < 4) {
+            constexpr int TPG = C / L::NG;
+            const int p = tid % L::DKP, grp = tid / L::DKP;
+            float gg[TPG], kk[TPG], qq[TPG];
+            if (grp < L::NG) {
+                float prod = 1.f;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float* row = st + (4 * grp + i) * L::ROW;
-                    g4[i] = row[2 * L::DKP + p]; k4[i] = row[p]; q4[i] = row[L::DKP + p];
+                for (int i = 0; i < TPG; ++i) {
+                    const float* row = st + (TPG * grp + i) * L::ROW;
+                    gg[i] = row[2 * L::DKP + p]; kk[i] = row[p]; qq[i] = row[L::DKP + p];
+                    prod *= gg[i];
                 }
-                ds_smem[L::GP_AT + grp * L::DKP + p] = g4[0] * g4[1] * g4[2] * g4[3];
+                if (L::NG > 1) ds_smem[L::GP_AT + grp * L::DKP + p] = prod;
             }
-            __syncthreads();
-            if (grp < 4) {
-                float pre = 1.f, post = 1.f;
+            if (L::NG > 1) __syncthreads();
+            if (grp < L::NG) {
+                float G = 1.f, suf = 1.f;
+                if (L::NG > 1) {
 #pragma unroll
-                for (int o = 0; o < 4; ++o) {
-                    const float x = ds_smem[L::GP_AT + o * L::DKP + p];
-                    if (o < grp) pre *= x;
-                    if (o > grp) post *= x;
+                    for (int o = 0; o < L::NG; ++o) {
+                        const float x = ds_smem[L::GP_AT + o * L::DKP + p];
+                        if (o < grp) G *= x;
+                        if (o > grp) suf *= x;
+                    }
                 }
-                float G = pre;
-                float suf[4];
-                suf[3] = post; suf[2] = suf[3] * g4[3]; suf[1] = suf[2] * g4[2]; suf[0] = suf[1] * g4[1];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float* row = st + (4 * grp + i) * L::ROW;
-                    G *= g4[i];
-                    row[2 * L::DKP + p] = k4[i] * G;
-                    row[L::DKP + p] = q4[i] * G;
-                    row[p] = k4[i] * suf[i];
+                for (int i = 0; i < TPG; ++i) {
+                    float* row = st + (TPG * grp + i) * L::ROW;
+                    G *= gg[i];
+                    row[2 * L::DKP + p] = kk[i] * G;
+                    row[L::DKP + p] = qq[i] * G;
                 }
-                if (grp == 3) ds_smem[L::GC_AT + p] = G;
+                if (grp == L::NG - 1) ds_smem[L::GC_AT + p] = G;
+#pragma unroll
+                for (int i = TPG - 1; i >= 0; --i) {
+                    st[(TPG * grp + i) * L::ROW + p] = kk[i] * suf;
+                    suf *= gg[i];
+                }
             }
         }
         __syncthreads();
-        // (2) what the state before the chunk gives token t's correction (lane t) and read-out (lane 16 + t): the column
-        // goes through shared memory, and a lane walks all of it against its token's G_t k_t or G_t q_t
-        float x;
+        // (2) what the state before the chunk gives token t's correction (lane t) and read-out (lane 16 + t): the columns
+        // go through shared memory, and a lane walks all of them against its token's G_t k_t or G_t q_t
+        float x[NC];
         {
-            float* sw = ds_smem + L::SW_AT + jl * L::DKP;
-            if constexpr (RP == 4) *reinterpret_cast<float4*>(sw + row0) = make_float4(S[0], S[1], S[2], S[3]);
-            else if constexpr (RP == 2) *reinterpret_cast<float2*>(sw + row0) = make_float2(S[0], S[1]);
-            else sw[row0] = S[0];
+            float* sw = ds_smem + L::SW_AT + jw * L::DKP;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                if constexpr (RP == 4) *reinterpret_cast<float4*>(sw + c * L::DKP + row0) = make_float4(S[c][0], S[c][1], S[c][2], S[c][3]);
+                else if constexpr (RP == 2) *reinterpret_cast<float2*>(sw + c * L::DKP + row0) = make_float2(S[c][0], S[c][1]);
+                else sw[c * L::DKP + row0] = S[c][0];
+            }
             __syncwarp();
             const float* xr = st + (lane & 15) * L::ROW + (lane < 16 ? 2 * L::DKP : L::DKP);
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            float acc[NC][4];
 #pragma unroll
+            for (int c = 0; c < NC; ++c) acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+#pragma unroll 8
             for (int m = 0; m < L::DKP / 4; ++m) {
                 const float4 xv = *reinterpret_cast<const float4*>(xr + 4 * m);
-                const float4 sv = *reinterpret_cast<const float4*>(sw + 4 * m);
-                a0 = fmaf(xv.x, sv.x, a0); a1 = fmaf(xv.y, sv.y, a1); a2 = fmaf(xv.z, sv.z, a2); a3 = fmaf(xv.w, sv.w, a3);
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    const float4 sv = *reinterpret_cast<const float4*>(sw + c * L::DKP + 4 * m);
+                    acc[c][0] = fmaf(xv.x, sv.x, acc[c][0]); acc[c][1] = fmaf(xv.y, sv.y, acc[c][1]);
+                    acc[c][2] = fmaf(xv.z, sv.z, acc[c][2]); acc[c][3] = fmaf(xv.w, sv.w, acc[c][3]);
+                }
             }
-            x = (a0 + a1) + (a2 + a3);
+#pragma unroll
+            for (int c = 0; c < NC; ++c) x[c] = (acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]);
         }
         // (3) lane t < 16: v_t minus the sum, times beta_t when its turn comes; lane 16 + t: the read-out so far
-        float u[C];
+        float u[NC][C];
         const float* mine = st + (lane & 15) * L::ROW;
         const float beta = lane < 16 ? mine[L::BETA_AT] : 0.f;
-        if (lane < 16) x = (col ? mine[L::V_AT + jl] : 0.f) - x;
+        if (lane < 16) {
+#pragma unroll
+            for (int c = 0; c < NC; ++c) x[c] = (j0 + jw + c < a.dv ? mine[L::V_AT + jw + c] : 0.f) - x[c];
+        }
 #pragma unroll
         for (int q = 0; q < C; ++q) {
-            u[q] = __shfl_sync(0xffffffffu, beta * x, q);
-            x = fmaf(st[q * L::ROW + L::AB_AT + lane], u[q], x);
+            const float coef = st[q * L::ROW + L::AB_AT + lane];
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                u[c][q] = __shfl_sync(0xffffffffu, beta * x[c], q);
+                x[c] = fmaf(coef, u[c][q], x[c]);
+            }
         }
-        if (col && lane >= 16 && lane - 16 < n) a.o[(size_t)(tb + lane - 16) * a.o_stride + h * a.dv + j] = x;
+        if (lane >= 16 && lane - 16 < n) {
+            float* dst = a.o + (size_t)(tb + lane - 16) * a.o_stride + h * a.dv + j0 + jw;
+#pragma unroll
+            for (int c = 0; c < NC; ++c)
+                if (j0 + jw + c < a.dv) dst[c] = x[c];
+        }
         // (4) the state behind the chunk
         {
             float gc[RP];
             load_rows<RP>(ds_smem + L::GC_AT + row0, gc);
 #pragma unroll
-            for (int i = 0; i < RP; ++i) S[i] *= gc[i];
+            for (int c = 0; c < NC; ++c)
+#pragma unroll
+                for (int i = 0; i < RP; ++i) S[c][i] *= gc[i];
         }
 #pragma unroll
         for (int t = 0; t < C; ++t) {
             float kt[RP];
             load_rows<RP>(st + t * L::ROW + row0, kt);
 #pragma unroll
-            for (int i = 0; i < RP; ++i) S[i] = fmaf(kt[i], u[t], S[i]);
+            for (int c = 0; c < NC; ++c)
+#pragma unroll
+                for (int i = 0; i < RP; ++i) S[c][i] = fmaf(kt[i], u[c][t], S[c][i]);
         }
         __syncthreads();
     }
-    if (col) {
+#pragma unroll
+    for (int c = 0; c < NC; ++c)
 #pragma unroll
         for (int i = 0; i < RP; ++i)
-            if (row0 + i < a.dk) sp[i] = S[i];
-    }
+            if (j0 + jw + c < a.dv && row0 + i < a.dk) sp[(size_t)c * a.dk + i] = S[c][i];
 }
 
 template <int RP>
@@ -576,8 +630,8 @@ static int delta_scan_chunked(const DeltaScanArgs& a, float* ab, dim3 grid, int 
         set[vec] = true;
     }
     idm_launch(delta_pairs_kernel, dim3((max_tokens + DC_C - 1) / DC_C, grid.y, grid.z), dim3(128), 0, stream, a, ab);
-    if (vec) idm_launch(delta_scan_chunked_kernel<RP, true>, grid, dim3(DS_COLS * 32), smem, stream, a, (const float*)ab);
-    else idm_launch(delta_scan_chunked_kernel<RP, false>, grid, dim3(DS_COLS * 32), smem, stream, a, (const float*)ab);
+    if (vec) idm_launch(delta_scan_chunked_kernel<RP, true>, grid, dim3(DeltaChunk<RP>::NT), smem, stream, a, (const float*)ab);
+    else idm_launch(delta_scan_chunked_kernel<RP, false>, grid, dim3(DeltaChunk<RP>::NT), smem, stream, a, (const float*)ab);
     return 0;
 }
 

@@ -290,7 +290,7 @@ read_model_dir = read_lunulix        # (config dict, tensors by name) of any mod
 # ------------------------------------------------------------------------------------- Fuginex
 def fuginex_parallel(heads=4, kv_heads=2, dim=16, scale=0.3, window=20, rot_dims=8, rot_base=5000.0,
                      scaling=(4.0, 64, 8.0, 1.0), r_heads=4, r_kv_heads=2, r_dim=12, r_vdim=20, conv=3, ranks=(8, 16),
-                     left_scale=1.2, right_scale=0.9, ff=48, weights_of=None):
+                     left_scale=1.3, right_scale=0.9, ff=48, weights_of=None):
     """One ``parallel`` layer of a Fuginex config.json; every size and constant is an argument.  ``scaling``: (factor,
     original, fast, slow) or None; ``ranks``: the two low-rank sizes, or None to leave them to the tensors."""
     left = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=scale)
@@ -373,8 +373,8 @@ def fuginex_random_config(seed: int) -> dict:
                                 scaling=r.choice([None, (2.0, 1024, 16.0, 1.0), (8.0, 64, 4.0, 0.5), (16.0, 256, 8.0, 2.0)]) if rot else None,
                                 r_heads=rkv * r.choice([1, 2]), r_kv_heads=rkv, r_dim=r.choice([16, 32, 40, 64, 128]),
                                 r_vdim=r.choice([16, 24, 32, 64, 128]), conv=r.choice([1, 2, 3, 4]),
-                                ranks=r.choice([None, (8, 8), (24, 16), (12, 40)]), left_scale=r.choice([1.0, 1.2, 0.4]),
-                                right_scale=r.choice([1.0, 1.1, 0.7]), ff=r.choice([None, 64, 160, 256]))
+                                ranks=r.choice([None, (8, 8), (24, 16), (12, 40)]), left_scale=r.choice([1.0, 1.3, 0.4]),
+                                right_scale=r.choice([1.0, 0.8, 0.7]), ff=r.choice([None, 64, 160, 256]))
     layers = [layer() for _ in range(r.choice([1, 2, 3]))]
     for _ in range(r.choice([0, 1, 2])):
         layers.insert(r.randrange(1, len(layers) + 1), dict(weights_of=None))      # filled in below

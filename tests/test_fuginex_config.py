@@ -24,7 +24,7 @@ def test_every_key_is_read_per_layer():
     par, att = spec.layers[0], spec.layers[1]
     assert par.kind == att.kind == "parallel_residual" and par.prefix == "l0." and att.prefix == "l1."
     left, right = par.mixer.branches[0], par.mixer.branches[1]
-    assert (left.scale, right.scale, par.mixer.prefix, left.prefix) == (1.2, 0.9, "mix.", "left.")
+    assert (left.scale, right.scale, par.mixer.prefix, left.prefix) == (1.3, 0.9, "mix.", "left.")
     l, r = left.mixer, right.mixer
     assert (l.n_heads, l.n_kv_heads, l.key_dim, l.value_dim, l.softmax_scale, l.window) == (4, 2, 16, 16, 0.3, 20)
     assert l.unit_sink and l.values_from_keys and l.bias_in and l.bias_out and not l.head_gate and l.slope_exponent is None
