@@ -39,8 +39,8 @@ def softplus(z: torch.Tensor) -> torch.Tensor:
 
 
 def causal_conv(u: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """u [T, C], w [C, taps]: y_t = sum_j w[:, j] u_(t - taps + 1 + j), zeros before the start; the last
-    column of w multiplies the current token."""
+    """u [T, C], w [C, taps]: y_t = sum_j w[:, j] u_(t - taps + 1 + j) with u = 0 at negative indices, so that
+    w[:, taps - 1] is the factor of u_t itself."""
     T, C = u.shape
     taps = w.shape[1]
     pad = torch.cat([torch.zeros(taps - 1, C, dtype=u.dtype), u], dim=0)
