@@ -578,7 +578,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64 and the 32-bit check")
     ap.add_argument("--skip-sizes", action="store_true", help="leave out the points at 8B and 32B layer sizes")
     ap.add_argument("--design", default="", choices=["", "lunulix", "panodra", "fuginex"],
-                    help="instead of the default workload: this design beside qwen3 at equal layer sizes")
+                    help="instead of the default workload: this design beside its closest other one at equal layer sizes")
     ap.add_argument("--design-sizes", default="0.6b,8b", help="layer sizes of --design (presets <design>-<size>)")
     args = ap.parse_args()
     if args.gpus != 1:
