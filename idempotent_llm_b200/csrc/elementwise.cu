@@ -191,6 +191,59 @@ __global__ void __launch_bounds__(256) add_rmsnorm2_kernel(float* __restrict__ h
     }
 }
 
+// The same for rows of at most NV * 1024 elements with hidden % 4 == 0: a thread owns NV pieces of four consecutive
+// elements in registers (no staging in shared memory), all of its loads of the stream in flight at once.
+template <int NV>
+__global__ void __launch_bounds__(256) add_rmsnorm2_vec4_kernel(float* __restrict__ h, const float* __restrict__ delta, int n_partials,
+                                                                size_t partial_stride, const float* __restrict__ gamma1,
+                                                                const float* __restrict__ gamma2, float eps, T* __restrict__ x1,
+                                                                T* __restrict__ x2, const float* __restrict__ post, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int c = (threadIdx.x + 256 * k) * 4;
+        v[k] = c < hidden ? *reinterpret_cast<const float4*>(h + (size_t)r * hidden + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int c = (threadIdx.x + 256 * k) * 4;
+        if (c < hidden) {
+            const size_t idx = (size_t)r * hidden + c;
+            for (int p = 0; p < n_partials; ++p) {
+                const float4 d = *reinterpret_cast<const float4*>(delta + p * partial_stride + idx);
+                v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
+            }
+            if (post) {
+                const float4 b = *reinterpret_cast<const float4*>(post + c);
+                *reinterpret_cast<float4*>(h + idx) = make_float4(v[k].x + b.x, v[k].y + b.y, v[k].z + b.z, v[k].w + b.w);
+            } else if (n_partials) {
+                *reinterpret_cast<float4*>(h + idx) = v[k];
+            }
+            ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+        }
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int c = (threadIdx.x + 256 * k) * 4;
+        if (c < hidden) {
+            const float4 g1 = *reinterpret_cast<const float4*>(gamma1 + c);
+            const float nx = v[k].x * inv, ny = v[k].y * inv, nz = v[k].z * inv, nw = v[k].w * inv;
+            store4(x1 + (size_t)r * hidden + c, nx * g1.x, ny * g1.y, nz * g1.z, nw * g1.w);
+            if (x2) {
+                const float4 g2 = *reinterpret_cast<const float4*>(gamma2 + c);
+                store4(x2 + (size_t)r * hidden + c, nx * g2.x, ny * g2.y, nz * g2.z, nw * g2.w);
+            }
+        }
+    }
+}
+
 extern "C" int idm_add_rmsnorm2(float* h, const float* delta, int n_partials, long long partial_stride,
                                 const float* gamma1, const float* gamma2, float eps, void* x1, void* x2,
                                 const float* post, int n_rows, int hidden, cudaStream_t stream) {
@@ -198,6 +251,22 @@ extern "C" int idm_add_rmsnorm2(float* h, const float* delta, int n_partials, lo
     IDM_REQUIRE(hidden > 0 && n_rows > 0, "add_rmsnorm2: bad sizes rows=%d hidden=%d", n_rows, hidden);
     IDM_REQUIRE((size_t)hidden * 4 <= 160 * 1024, "add_rmsnorm2: hidden=%d does not fit shared memory", hidden);
     IDM_REQUIRE((gamma2 == nullptr) == (x2 == nullptr), "add_rmsnorm2: a second weight and a second output come together");
+    if (hidden % 4 == 0 && hidden <= 4096 && (partial_stride % 4) == 0) {
+        // NOTE: the sum of squares is taken over the same values in another thread layout than the general kernel's;
+        // which kernel runs depends on `hidden` only
+        const int np = delta ? n_partials : 0;
+        if (hidden <= 1024)
+            idm_launch(add_rmsnorm2_vec4_kernel<1>, dim3(n_rows), dim3(256), 0, stream, h, delta, np, (size_t)partial_stride,
+                       gamma1, gamma2, eps, (T*)x1, (T*)x2, post, hidden);
+        else if (hidden <= 2048)
+            idm_launch(add_rmsnorm2_vec4_kernel<2>, dim3(n_rows), dim3(256), 0, stream, h, delta, np, (size_t)partial_stride,
+                       gamma1, gamma2, eps, (T*)x1, (T*)x2, post, hidden);
+        else
+            idm_launch(add_rmsnorm2_vec4_kernel<4>, dim3(n_rows), dim3(256), 0, stream, h, delta, np, (size_t)partial_stride,
+                       gamma1, gamma2, eps, (T*)x1, (T*)x2, post, hidden);
+        IDM_LAUNCH_CHECK("add_rmsnorm2");
+        return 0;
+    }
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(add_rmsnorm2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

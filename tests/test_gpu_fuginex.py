@@ -365,7 +365,7 @@ def test_parallel_mixer_is_the_weighted_sum_of_its_branches(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("hidden", [20, 96, 2048])
+@pytest.mark.parametrize("hidden", [18, 20, 96, 1028, 2048, 4096, 4100])
 def test_two_norms_of_one_row_in_one_pass(dtype, hidden):
     K = _rt(dtype).kernels
     g = torch.Generator().manual_seed(2)
