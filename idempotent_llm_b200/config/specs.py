@@ -94,6 +94,18 @@ class NormSpec:
 
 
 @dataclass(frozen=True)
+class LayerNormSpec:
+    """Layer norm over the last axis: ``(x - mean) / sqrt(mean((x - mean)^2) + eps) * w + b``.  The weight is ``prefix +
+    weight``, the bias that name plus ``bias_suffix``."""
+
+    size: int
+    eps: float
+    weight: str = "weight"
+    bias_suffix: str = ".b"
+    kind: str = "layernorm"
+
+
+@dataclass(frozen=True)
 class AttentionNames:
     """Checkpoint names of an attention layer's tensors, behind the layer's prefix.  An architecture's
     configuration sets them; the part has none of its own."""
@@ -228,6 +240,34 @@ class TableExpertsSpec:
 
 
 @dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """``n_experts`` small gated feed-forwards ``down_e(act(gate_e x) * up_e x)`` and ``n_identity`` experts that hand
+    their input on, of which a token uses ``top``, named by a learned router.  With ``z = W_r x`` over all ``n_experts +
+    n_identity`` outputs (32-bit): ``s = softmax(z)``; experts are CHOSEN by ``s + correction`` (a learned row), the
+    ``top`` largest among the experts of the ``groups_keep`` best of ``groups`` equal groups of neighbours (a group's
+    score: its largest choice score); the WEIGHTS are the chosen experts' ``s`` over their sum (+ 1e-20), times
+    ``scale``.  ``shared``: a gated feed-forward of the same form that every token runs, added to the sum.  Expert e's
+    tensors are ``prefix + expert.format(e) + gate / up / down``; identity experts are the router's last outputs and
+    have no tensors."""
+
+    hidden: int
+    intermediate: int
+    n_experts: int
+    top: int
+    n_identity: int = 0
+    groups: int = 1
+    groups_keep: int = 1
+    scale: float = 1.0
+    activation: str = "silu"
+    shared: Optional["GatedMLPSpec"] = None
+    router: str = "router"
+    correction: str = "correction"
+    expert: str = "e{}."
+    names: GatedMLPNames = GatedMLPNames(gate="gate", up="up", down="down")
+    kind: str = "routed_experts"
+
+
+@dataclass(frozen=True)
 class SinkAttentionNames:
     """Checkpoint names of a gated attention with short filters and a sink, behind the mixer's prefix; a filter's
     tensor is its projection's name plus ``conv``."""
@@ -312,6 +352,7 @@ class HeadAttentionNames:
     k_norm: str = "k.norm"
     gate: str = "g"
     bias: str = ".b"
+    sink: str = "sink"
 
 
 @dataclass(frozen=True)
@@ -321,9 +362,12 @@ class HeadAttentionSpec:
     ``"half_partial"``).  Each of the following is an option: biases on the input projections (``bias_in``) and on
     the output projection (``bias_out``); ``values_from_keys``: there is no value projection, a token's value is its
     key as projected (with bias, before norm and rotation); ``window`` of W: a query at p sees keys p - W + 1 .. p;
-    ``unit_sink``: the softmax's denominator has one more term of score 0 and no value; ``slope_exponent`` c: head h
-    of H takes ``2^(-c (h + 1) / H)`` times the distance to a key off its score; ``head_gate``: a head's output times
-    ``sigmoid`` of one number per head projected from the mixer's input."""
+    ``unit_sink``: the softmax's denominator has one more term of score 0 and no value; ``sink``: that term's score is a
+    learned number per head instead (tensor ``names.sink`` [heads]; it is neither scaled nor capped); ``keep_first`` of F
+    (with a window): a query also sees the sequence's first F keys, however far back; ``softcap`` c: a score becomes
+    ``c tanh(score / c)`` after the scale; ``slope_exponent`` c: head h of H takes ``2^(-c (h + 1) / H)`` times the
+    distance to a key off its score; ``head_gate``: a head's output times ``sigmoid`` of one number per head projected
+    from the mixer's input."""
 
     hidden: int
     n_heads: int
@@ -341,6 +385,9 @@ class HeadAttentionSpec:
     values_from_keys: bool = False
     bias_in: bool = False
     bias_out: bool = False
+    sink: bool = False
+    keep_first: int = 0
+    softcap: Optional[float] = None
     names: HeadAttentionNames = HeadAttentionNames()
     kind: str = "head_attention"
 
@@ -361,6 +408,8 @@ class DeltaRuleNames:
     dt_bias: str = "dt_bias"
     gate_down: str = "g1"
     gate_up: str = "g2"
+    decay: str = "a"
+    gate: str = "g"
     norm: str = "norm"
     o: str = "o"
 
@@ -374,7 +423,12 @@ class DeltaRuleSpec:
     exp(-exp(A_log_h) softplus(W_a2 W_a1 h + dt_bias))`` per head and key channel; the read-out is divided by its
     root mean square over ``value_dim`` (``norm_eps``), times a weight ``[value_dim]``, times ``sigmoid(W_g2 W_g1
     h)``.  ``decay_rank`` / ``gate_rank`` are the inner sizes of the two low-rank projections; None: whatever the
-    checkpoint's tensors have (random weights then take ``key_dim // 2`` rounded up to 8)."""
+    checkpoint's tensors have (random weights then take ``key_dim // 2`` rounded up to 8).
+
+    ``decay`` ``"head"`` instead of ``"channel"``: one decay per head, ``g = exp(-exp(A_log_h) softplus(W_a h + dt_bias_h))``
+    with a full matrix ``names.decay`` [heads, hidden] and ``dt_bias`` [heads].  ``gate`` ``"silu"`` instead of
+    ``"sigmoid_low_rank"``: the read-out times ``silu(W_g h)`` with a full matrix ``names.gate`` [heads * value_dim,
+    hidden]."""
 
     hidden: int
     heads: int
@@ -385,6 +439,8 @@ class DeltaRuleSpec:
     norm_eps: float
     decay_rank: Optional[int] = None
     gate_rank: Optional[int] = None
+    decay: str = "channel"
+    gate: str = "sigmoid_low_rank"
     names: DeltaRuleNames = DeltaRuleNames()
     kind: str = "gated_delta"
 
@@ -448,6 +504,36 @@ class SandwichLayerSpec:
 
 
 @dataclass(frozen=True)
+class PostNormLayerSpec:
+    """A layer whose sublayers read the stream itself and whose norms sit BEHIND them: ``h += s1 * N1(mixer(h))``,
+    then, if it has a feed-forward, ``h += s2 * N2(ff(h))``.  ``mixer_scale`` / ``feed_forward_scale`` name learned rows
+    ``[hidden]`` (None: no scale).  The norms' tensors are ``prefix + <spec.weight>``."""
+
+    prefix: str
+    mixer: object
+    mixer_post_norm: object
+    feed_forward: Optional[object] = None
+    feed_forward_post_norm: Optional[object] = None
+    mixer_scale: Optional[str] = None
+    feed_forward_scale: Optional[str] = None
+    kind: str = "postnorm"
+
+
+@dataclass(frozen=True)
+class BigramHashSpec:
+    """A token embedding with a hashed bigram row added: ``E[token_t] + B[(mul_prev * token_(t-1) + mul_cur * token_t)
+    mod buckets]``, and ``B[buckets]`` (the table's last row) for a sequence's first token.  A sequence's last token is
+    part of its state between steps."""
+
+    hidden: int
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    table: str = "bigram"
+    kind: str = "bigram_hash"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One layer: which block arrangement, and the parts inside it.
 
@@ -504,6 +590,7 @@ class ModelSpec:
     mix_in_name: Optional[str] = None   # the matrix of the schedule's `mix_in` stops
     logit_scale: float = 1.0            # logits are multiplied with this constant, then
     logit_softcap: Optional[float] = None   # capped: cap * tanh(logits / cap)
+    embedding: Optional[object] = None      # a registered kind of token embedding (``BigramHashSpec``); None: a plain lookup
     extra: dict = field(default_factory=dict, compare=False)
 
     def __post_init__(self):

@@ -3,7 +3,9 @@
 // one warp per (token, q-head), all arithmetic in 32-bit.
 //
 // A query at position p of sequence s sees keys j with max(0, p - window + 1) <= j <= p
-// (window <= 0: all j <= p), the slot-causal rule of src/detllm/model.py:259-266.
+// (window <= 0: all j <= p), the slot-causal rule of src/detllm/model.py:259-266; with keep_first > 0 also the
+// keys j < keep_first, however far back they lie (the blocks of 32 that hold them are walked first, then the
+// window's).  softcap > 0 bounds a score: cap * tanh(score / cap), after the scale and before the softmax.
 // Keys are walked in blocks of 32 aligned to absolute positions; inside a block lane i
 // scores key j0 + i; masked lanes contribute exactly 0 and are left out of the maximum
 // (the float analogue of the reference's integer sentinel, src/detllm/ops/di_softmax.py:45-58);
@@ -30,6 +32,8 @@ struct AttnArgs {
     float out_scale;
     const float* slopes;          // [n_q] or null: slopes[head] * (p - j) is taken off the score of key j
     int gate_per_head;            // the gate is one number per head: gate[t * gate_stride + head]
+    float softcap;                // > 0: score <- softcap * tanh(score / softcap)
+    int keep_first;               // > 0: keys j < keep_first are seen from any distance
 };
 
 #define AG_WARPS 4
@@ -55,9 +59,12 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(AttnAr
     float acc[IDM_MAX_HEAD_DIM / 32];
 #pragma unroll
     for (int i = 0; i < IDM_MAX_HEAD_DIM / 32; ++i) acc[i] = 0.f;
-    for (int j0 = (lo / 32) * 32; j0 <= pos; j0 += 32) {
+    const int keep = a.window > 0 ? min(a.keep_first, lo) : 0;     // kept keys below the window's first
+    const int lo0 = (lo / 32) * 32, keep_end = min(((keep + 31) / 32) * 32, lo0);
+    for (int j0 = keep > 0 ? 0 : lo0; j0 <= pos; j0 += 32) {
+        if (j0 == keep_end && j0 < lo0) j0 = lo0;               // from the kept keys' last block on to the window's first
         const int j = j0 + lane;
-        const bool valid = j >= lo && j <= pos;
+        const bool valid = (j >= lo || j < keep) && j <= pos;
         float sc = -INFINITY;
         const T* vrow = nullptr;
         if (valid) {
@@ -80,6 +87,7 @@ __global__ void __launch_bounds__(AG_WARPS * 32) attention_generic_kernel(AttnAr
                 for (int d = 0; d < a.hd; ++d) dot = fmaf(qs[d], to_f32(krow[d]), dot);
             }
             sc = dot * a.scale;
+            if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
             if (a.slopes) sc -= a.slopes[head] * (float)(pos - j);
         }
         const float m_new = fmaxf(m, warp_max(sc));
@@ -143,7 +151,7 @@ extern "C" int idm_attention_generic(const void* q, void* out, void* k_pool, voi
     a.token_seq = token_seq; a.positions = positions; a.slots = slots; a.q_start = q_start; a.cu_q = cu_q;
     a.n_tokens = n_tokens; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd; a.scale = scale; a.window = window;
     a.dv = hd; a.sink = nullptr; a.gate = nullptr; a.gate_stride = 0; a.out_stride = n_q * hd; a.out_col = 0; a.out_scale = 1.f;
-    a.slopes = nullptr; a.gate_per_head = 0;
+    a.slopes = nullptr; a.gate_per_head = 0; a.softcap = 0.f; a.keep_first = 0;
     return attention_generic_launch(a, stream);
 }
 
@@ -171,25 +179,29 @@ extern "C" int idm_attention_sink(const void* q, void* out, int out_stride, int 
     a.n_tokens = n_tokens; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd; a.scale = scale; a.window = window;
     a.dv = dv; a.sink = sink; a.gate = gate; a.gate_stride = gate_stride; a.out_stride = out_stride; a.out_col = out_col;
     a.out_scale = out_scale;
-    a.slopes = nullptr; a.gate_per_head = 0;
+    a.slopes = nullptr; a.gate_per_head = 0; a.softcap = 0.f; a.keep_first = 0;
     return attention_generic_launch(a, stream);
 }
 
 // The same walk once more with every option this kernel has: a window over a cache that keeps all keys (ring 0) or
-// a ring, a sink, a slope per head whose product with the distance p - j is taken off the score, and a gate that is
-// one number per head (gate_per_head) or one per channel.
+// a ring, a sink, a slope per head whose product with the distance p - j is taken off the score, a gate that is
+// one number per head (gate_per_head) or one per channel, a cap on the scores and first keys that every query sees
+// (keep_first; not with a ring, which does not keep them).
 extern "C" int idm_attention_biased(const void* q, void* out, int out_stride, int out_col, float out_scale,
                                     void* k_pool, void* v_pool, const int* table, int table_stride, int ring,
                                     const float* sink, const float* slopes, const float* gate, int gate_stride,
                                     int gate_per_head, const int* token_seq, const int* positions, const int* slots,
                                     const int* q_start, const int* cu_q, int n_tokens, int n_q, int n_kv,
-                                    int hd, int dv, float scale, int window, cudaStream_t stream) {
+                                    int hd, int dv, float scale, int window, float softcap, int keep_first,
+                                    cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     IDM_REQUIRE(hd > 0 && hd <= IDM_MAX_HEAD_DIM && dv > 0 && dv <= IDM_MAX_HEAD_DIM,
                 "attention: key and value sizes %d, %d must be at most %d", hd, dv, IDM_MAX_HEAD_DIM);
     IDM_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "attention: %d q-heads are no multiple of %d kv-heads", n_q, n_kv);
     IDM_REQUIRE(out_col >= 0 && out_col + n_q * dv <= out_stride, "attention: columns %d..%d of rows of %d", out_col,
                 out_col + n_q * dv, out_stride);
+    IDM_REQUIRE(keep_first >= 0 && softcap >= 0.f && (keep_first == 0 || ring == 0),
+                "attention: keep_first=%d softcap=%g ring=%d (a ring does not keep a sequence's first keys)", keep_first, softcap, ring);
     AttnArgs a;
     a.q = (const T*)q; a.out = (T*)out;
     a.cache = KVAddr{(T*)k_pool, (T*)v_pool, table, table_stride, ring, n_kv, hd};
@@ -198,5 +210,6 @@ extern "C" int idm_attention_biased(const void* q, void* out, int out_stride, in
     a.n_tokens = n_tokens; a.n_q = n_q; a.n_kv = n_kv; a.hd = hd; a.scale = scale; a.window = window;
     a.dv = dv; a.sink = sink; a.gate = gate; a.gate_stride = gate_stride; a.out_stride = out_stride; a.out_col = out_col;
     a.out_scale = out_scale; a.slopes = slopes; a.gate_per_head = gate_per_head;
+    a.softcap = softcap; a.keep_first = keep_first;
     return attention_generic_launch(a, stream);
 }

@@ -143,14 +143,14 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 }
 
 // Gated activations by number.  act 0: g * sigmoid(g) * u (silu_mul);  act 1: the tanh form of gelu,
-// 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u.  One formula each, wherever it is applied: the epilogue
+// 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u;  act 2: max(g, 0) * u.  One formula each, wherever it is applied: the epilogue
 // of a gate/up product and the kernel of its own give the same bits.
 __device__ __forceinline__ float gelu_tanh_f(float g) {
     const float inner = 0.7978845608028654f * fmaf(0.044715f * g * g, g, g);
     return 0.5f * g * (1.0f + tanhf(inner));
 }
 __device__ __forceinline__ float gated_act(float g, float u, int act) {
-    return act == 1 ? gelu_tanh_f(g) * u : silu_mul(g, u);
+    return act == 1 ? gelu_tanh_f(g) * u : act == 2 ? fmaxf(g, 0.f) * u : silu_mul(g, u);
 }
 
 // ------------------------------------------------------------ reductions

@@ -41,10 +41,12 @@ extern "C" int idm_cols_cast(const float* in, int stride, int col0, int width, v
 // c [N, c_stride]: filtered and activated q (Hk x dk at c_q), k (at c_k); both become unit vectors per head,
 // x / sqrt(sum x^2 + 1e-6), q also times dk^-1/2.  a [N, a_stride]: columns [a_col, a_col + H dk) hold the decay's
 // projection and become g = exp(-exp(A_log[h]) * softplus(a + dt_bias)).  beta[t, h] = sigmoid(proj[t, b_col + h]).
+// With one decay per head (head_col >= 0) the projection is proj[t, head_col + h], dt_bias has H entries, and the
+// head's decay is written to all dk of its columns of `a`, which the recurrence reads as it reads decays per channel.
 struct DeltaPrepArgs {
     float* c; int c_stride, c_q, c_k;
     float* a; int a_stride, a_col;
-    const float* proj; int p_stride, b_col;
+    const float* proj; int p_stride, b_col, head_col;
     const float* dt_bias; const float* a_log;
     float* beta;
     int H, Hk, dk;
@@ -68,19 +70,21 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(DeltaPrepArgs p) {
     }
     float* arow = p.a + (size_t)t * p.a_stride + p.a_col;
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < p.H * p.dk; i += gridDim.y * blockDim.x) {
-        const float rate = expf(p.a_log[i / p.dk]);
-        arow[i] = expf(-rate * softplus_f(arow[i] + p.dt_bias[i]));
+        const int hh = i / p.dk;
+        const float rate = expf(p.a_log[hh]);
+        const float z = p.head_col >= 0 ? p.proj[(size_t)t * p.p_stride + p.head_col + hh] + p.dt_bias[hh] : arow[i] + p.dt_bias[i];
+        arow[i] = expf(-rate * softplus_f(z));
     }
     for (int h = blockIdx.y * blockDim.x + threadIdx.x; h < p.H; h += gridDim.y * blockDim.x)
         p.beta[(size_t)t * p.H + h] = 1.0f / (1.0f + expf(-p.proj[(size_t)t * p.p_stride + p.b_col + h]));
 }
 
 extern "C" int idm_delta_prep(float* c, int c_stride, int c_q, int c_k, float* a, int a_stride, int a_col,
-                              const float* proj, int p_stride, int b_col, const float* dt_bias, const float* a_log,
+                              const float* proj, int p_stride, int b_col, int head_col, const float* dt_bias, const float* a_log,
                               float* beta, int H, int Hk, int dk, int n_tokens, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     IDM_REQUIRE(H > 0 && Hk > 0 && H % Hk == 0 && dk > 0, "delta_prep: %d heads over %d key heads of %d", H, Hk, dk);
-    DeltaPrepArgs p{c, c_stride, c_q, c_k, a, a_stride, a_col, proj, p_stride, b_col, dt_bias, a_log, beta, H, Hk, dk};
+    DeltaPrepArgs p{c, c_stride, c_q, c_k, a, a_stride, a_col, proj, p_stride, b_col, head_col, dt_bias, a_log, beta, H, Hk, dk};
     int split = (296 + n_tokens - 1) / n_tokens;
     const int most = (H * dk + 127) / 128;
     if (split > most) split = most;
@@ -679,12 +683,12 @@ extern "C" int idm_delta_scan(const float* c, int c_stride, int c_q, int c_k, in
 }
 
 // ------------------------------------------------------------------ behind the recurrence
-// out[t, out_col + h dv + j] = o[t, h, j] / sqrt(mean_j o^2 + eps) * w[j] * sigmoid(gate[t, gate_col + h dv + j]) * scale,
-// one warp per (token, head)
+// out[t, out_col + h dv + j] = o[t, h, j] / sqrt(mean_j o^2 + eps) * w[j] * act(gate[t, gate_col + h dv + j]) * scale,
+// act = sigmoid (gate_act 0) or silu (gate_act 1); one warp per (token, head)
 __global__ void __launch_bounds__(128) delta_out_kernel(const float* __restrict__ o, int o_stride, const float* __restrict__ w,
                                                         float eps, const float* __restrict__ gate, int gate_stride,
-                                                        int gate_col, float scale, T* __restrict__ out, int out_stride,
-                                                        int out_col, int n_tokens, int H, int dv) {
+                                                        int gate_col, int gate_act, float scale, T* __restrict__ out,
+                                                        int out_stride, int out_col, int n_tokens, int H, int dv) {
     pdl_launch_dependents();
     pdl_wait();
     const long long i = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -697,19 +701,21 @@ __global__ void __launch_bounds__(128) delta_out_kernel(const float* __restrict_
     const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
     const float* gr = gate + (size_t)t * gate_stride + gate_col + (size_t)h * dv;
     T* dst = out + (size_t)t * out_stride + out_col + (size_t)h * dv;
-    for (int d = lane; d < dv; d += 32)
-        from_f32(dst[d], x[d] * inv * w[d] / (1.0f + expf(-gr[d])) * scale);
+    for (int d = lane; d < dv; d += 32) {
+        const float z = gr[d], sg = 1.0f / (1.0f + expf(-z));
+        from_f32(dst[d], gate_act == 1 ? x[d] * inv * w[d] * (z * sg) * scale : x[d] * inv * w[d] / (1.0f + expf(-z)) * scale);
+    }
 }
 
 extern "C" int idm_delta_out(const float* o, int o_stride, const float* w, float eps, const float* gate, int gate_stride,
-                             int gate_col, float scale, void* out, int out_stride, int out_col, int n_tokens, int H,
+                             int gate_col, int gate_act, float scale, void* out, int out_stride, int out_col, int n_tokens, int H,
                              int dv, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     IDM_REQUIRE(H > 0 && dv > 0 && out_col >= 0 && out_col + H * dv <= out_stride, "delta_out: columns %d..%d of rows of %d",
                 out_col, out_col + H * dv, out_stride);
     const long long warps = (long long)n_tokens * H;
     idm_launch(delta_out_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, stream, o, o_stride, w, eps, gate,
-               gate_stride, gate_col, scale, (T*)out, out_stride, out_col, n_tokens, H, dv);
+               gate_stride, gate_col, gate_act, scale, (T*)out, out_stride, out_col, n_tokens, H, dv);
     IDM_LAUNCH_CHECK("delta_out");
     return 0;
 }

@@ -634,7 +634,7 @@ __global__ void __launch_bounds__(256) gated_act_kernel(const float* __restrict_
 
 extern "C" int idm_gated_act(const float* gu, void* y, int n_tokens, int inter, int act, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
-    IDM_REQUIRE(inter > 0 && (act == 0 || act == 1), "gated_act: inter=%d act=%d", inter, act);
+    IDM_REQUIRE(inter > 0 && act >= 0 && act <= 2, "gated_act: inter=%d act=%d", inter, act);
     idm_launch(gated_act_kernel, dim3(n_tokens, (inter + 255) / 256), dim3(256), 0, stream, gu, (T*)y, inter, act);
     IDM_LAUNCH_CHECK("gated_act");
     return 0;

@@ -4,6 +4,12 @@
 // token's result does not depend on what else the step holds.  Steps of many tokens group their rows by expert
 // on the host and run one matrix product per expert instead; the kernels below then gather the rows
 // (rows_gather) and add the experts' outputs back in the order of a token's choices (experts_combine).
+//
+// A learned router names a token's experts on the device: then `tokens` holds the step's row numbers and `table` the
+// step's choices [rows, top], and `pair_w` [rows, top] (null: 1) is the weight of every (token, choice) beside the
+// constant `weight`.  Where an expert's activations are 32-bit numbers of these kernels' own, the pair's weight is
+// multiplied into them (the down product is linear); where the library's products make them, the weight is applied
+// when the experts' outputs are added.
 #include "common.cuh"
 
 __device__ __forceinline__ float row_dot(const T* __restrict__ w, const float* __restrict__ xs, int K, int lane, bool vec) {
@@ -66,7 +72,8 @@ __device__ __forceinline__ void row_dot2(const T* __restrict__ w0, const T* __re
 // "gate rows, then up rows" and "gate and up rows alternating" (the layout a gated product's epilogue reads).
 // A block has one (token, choice) and 8 rows f per pass of its warps.
 __global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restrict__ x, const int* __restrict__ tokens,
-                                                              const int* __restrict__ table, const T* __restrict__ gate_up, long long expert_stride,
+                                                              const int* __restrict__ table, const float* __restrict__ pair_w,
+                                                              const T* __restrict__ gate_up, long long expert_stride,
                                                               long long row_stride, long long up_off,
                                                               float* __restrict__ a, int width, int ff, int top, int n_experts,
                                                               int act) {
@@ -81,11 +88,12 @@ __global__ void __launch_bounds__(256) experts_gate_up_kernel(const T* __restric
     if (e < 0 || e >= n_experts) return;                     // (a table entry outside the experts: contributes nothing)
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool vec = (width * (int)sizeof(T)) % 16 == 0;
+    const float pw = pair_w ? pair_w[tk] : 1.f;
     for (int f = blockIdx.y * 8 + wib; f < ff; f += gridDim.y * 8) {
         const T* row = gate_up + (size_t)e * expert_stride + (size_t)f * row_stride;
         float g, u;
         row_dot2(row, row + up_off, xs, xs, width, lane, vec, g, u);
-        if (lane == 0) a[(size_t)tk * ff + f] = gated_act(g, u, act);
+        if (lane == 0) a[(size_t)tk * ff + f] = pair_w ? gated_act(g, u, act) * pw : gated_act(g, u, act);
     }
 }
 
@@ -127,12 +135,12 @@ __global__ void __launch_bounds__(256) experts_down_kernel(const float* __restri
     }
 }
 
-extern "C" int idm_experts_few(const void* x, const int* tokens, const int* table, const void* gate_up, long long expert_stride,
+extern "C" int idm_experts_few(const void* x, const int* tokens, const int* table, const float* pair_w, const void* gate_up, long long expert_stride,
                                long long row_stride, long long up_off, const void* down,
                                float* a, float* h, int n_tokens, int width, int ff, int top, int n_experts, int act,
                                float weight, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
-    IDM_REQUIRE(width > 0 && ff > 0 && top > 0 && n_experts > 0 && (act == 0 || act == 1), "experts: width=%d ff=%d top=%d experts=%d act=%d",
+    IDM_REQUIRE(width > 0 && ff > 0 && top > 0 && n_experts > 0 && (act >= 0 && act <= 2), "experts: width=%d ff=%d top=%d experts=%d act=%d",
                 width, ff, top, n_experts, act);
     IDM_REQUIRE((size_t)width * 4 <= 160 * 1024 && (size_t)top * ff * 4 <= 160 * 1024, "experts: width=%d or top * ff=%d does not fit shared memory",
                 width, top * ff);
@@ -142,7 +150,7 @@ extern "C" int idm_experts_few(const void* x, const int* tokens, const int* tabl
     // blocks along the rows: enough to fill the part for one token, fewer per token as tokens grow
     const int by1 = max(1, min((ff + 7) / 8, 592 / max(1, n_tokens * top)));
     const int by2 = max(1, min((width + 7) / 8, 592 / max(1, n_tokens)));
-    idm_launch(experts_gate_up_kernel, dim3(n_tokens * top, by1), dim3(256), s1, stream, (const T*)x, tokens, table, (const T*)gate_up,
+    idm_launch(experts_gate_up_kernel, dim3(n_tokens * top, by1), dim3(256), s1, stream, (const T*)x, tokens, table, pair_w, (const T*)gate_up,
                expert_stride, row_stride, up_off, a, width, ff, top, n_experts, act);
     IDM_LAUNCH_CHECK("experts_gate_up");
     idm_launch(experts_down_kernel, dim3(n_tokens, by2), dim3(256), s2, stream, (const float*)a, tokens, table, (const T*)down, h, width,
@@ -169,7 +177,8 @@ extern "C" int idm_rows_gather(const void* x, const int* src, void* out, int n_r
 
 // h[t, :] += weight * sum_k z[place[t, k], :] in ascending k  (z 32-bit: the experts' outputs, grouped rows)
 __global__ void __launch_bounds__(256) experts_combine_kernel(const float* __restrict__ z, const int* __restrict__ place,
-                                                              float* __restrict__ h, int width, int top, float weight) {
+                                                              const float* __restrict__ pair_w, float* __restrict__ h, int width,
+                                                              int top, float weight) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t t = blockIdx.x;
@@ -177,16 +186,16 @@ __global__ void __launch_bounds__(256) experts_combine_kernel(const float* __res
         float s = 0.f;
         for (int k = 0; k < top; ++k) {
             const int r = place ? place[t * top + k] : (int)(t * top + k);      // (no places: pair by pair as they lie)
-            if (r >= 0) s += z[(size_t)r * width + d];
+            if (r >= 0) s = pair_w ? fmaf(pair_w[t * top + k], z[(size_t)r * width + d], s) : s + z[(size_t)r * width + d];
         }
         h[t * width + d] += s * weight;
     }
 }
 
-extern "C" int idm_experts_combine(const float* z, const int* place, float* h, int n_tokens, int width, int top,
-                                   float weight, cudaStream_t stream) {
+extern "C" int idm_experts_combine(const float* z, const int* place, const float* pair_w, float* h, int n_tokens, int width,
+                                   int top, float weight, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
-    idm_launch(experts_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, z, place, h, width, top, weight);
+    idm_launch(experts_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, z, place, pair_w, h, width, top, weight);
     IDM_LAUNCH_CHECK("experts_combine");
     return 0;
 }
@@ -202,6 +211,7 @@ extern "C" int idm_experts_combine(const float* z, const int* place, float* h, i
 template <int MODE>
 __global__ void __launch_bounds__(256) experts_major_kernel(const T* __restrict__ x, const float* __restrict__ a_in,
                                                             const int* __restrict__ tokens, const int* __restrict__ table,
+                                                            const float* __restrict__ pair_w,
                                                             const T* __restrict__ w, long long expert_stride, long long row_stride,
                                                             long long up_off, float* __restrict__ out, int n_tokens, int top,
                                                             int K, int rows, int act) {
@@ -297,32 +307,36 @@ __global__ void __launch_bounds__(256) experts_major_kernel(const T* __restrict_
             if (lane == 0) {
 #pragma unroll
                 for (int tt = 0; tt < EX_TOKENS; ++tt)
-                    if (tt < np) out[(size_t)pairs[p0 + tt] * rows + r] = MODE == 0 ? gated_act(g[tt], u[tt], act) : g[tt];
+                    if (tt < np) {
+                        const int pr = pairs[p0 + tt];
+                        out[(size_t)pr * rows + r] = MODE == 0 ? (pair_w ? gated_act(g[tt], u[tt], act) * pair_w[pr] : gated_act(g[tt], u[tt], act)) : g[tt];
+                    }
             }
         }
     }
 }
 
 // z: [n_tokens * top, width] 32-bit scratch for the experts' outputs (then added to h pair by pair in ascending k)
-extern "C" int idm_experts_major(const void* x, const int* tokens, const int* table, const void* gate_up,
+extern "C" int idm_experts_major(const void* x, const int* tokens, const int* table, const float* pair_w, const void* gate_up,
                                  long long expert_stride, long long row_stride, long long up_off, const void* down,
                                  float* a, float* z, float* h, int n_tokens, int width, int ff, int top, int n_experts,
                                  int act, float weight, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
-    IDM_REQUIRE(width > 0 && ff > 0 && top > 0 && n_experts > 0 && (act == 0 || act == 1), "experts: width=%d ff=%d top=%d experts=%d act=%d",
+    IDM_REQUIRE(width > 0 && ff > 0 && top > 0 && n_experts > 0 && (act >= 0 && act <= 2), "experts: width=%d ff=%d top=%d experts=%d act=%d",
                 width, ff, top, n_experts, act);
     const size_t s1 = (size_t)EX_TOKENS * width * 4 + (size_t)n_tokens * top * 4, s2 = (size_t)EX_TOKENS * ff * 4 + (size_t)n_tokens * top * 4;
     IDM_REQUIRE(s1 <= 200 * 1024 && s2 <= 200 * 1024, "experts: width=%d or ff=%d with %d tokens does not fit shared memory", width, ff, n_tokens);
     if (s1 > 48 * 1024) cudaFuncSetAttribute(experts_major_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s1);
     if (s2 > 48 * 1024) cudaFuncSetAttribute(experts_major_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s2);
     const int by1 = max(1, min((ff + 7) / 8, 592 / n_experts)), by2 = max(1, min((width + 7) / 8, 592 / n_experts));
-    idm_launch(experts_major_kernel<0>, dim3(n_experts, by1), dim3(256), s1, stream, (const T*)x, (const float*)nullptr, tokens, table,
+    idm_launch(experts_major_kernel<0>, dim3(n_experts, by1), dim3(256), s1, stream, (const T*)x, (const float*)nullptr, tokens, table, pair_w,
                (const T*)gate_up, expert_stride, row_stride, up_off, a, n_tokens, top, width, ff, act);
     IDM_LAUNCH_CHECK("experts_major gate/up");
-    idm_launch(experts_major_kernel<1>, dim3(n_experts, by2), dim3(256), s2, stream, (const T*)nullptr, (const float*)a, tokens, table,
+    idm_launch(experts_major_kernel<1>, dim3(n_experts, by2), dim3(256), s2, stream, (const T*)nullptr, (const float*)a, tokens, table, (const float*)nullptr,
                (const T*)down, (long long)width * ff, (long long)ff, 0LL, z, n_tokens, top, ff, width, act);
     IDM_LAUNCH_CHECK("experts_major down");
-    idm_launch(experts_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)z, (const int*)nullptr, h, width, top, weight);
+    idm_launch(experts_combine_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)z, (const int*)nullptr, (const float*)nullptr, h,
+               width, top, weight);
     IDM_LAUNCH_CHECK("experts_combine");
     return 0;
 }
@@ -354,14 +368,14 @@ extern "C" int idm_experts_grouped(const void* xg, const int* counts, int n_expe
 // The grouped feed-forward of a step from one call: rows gathered in the order of their experts (src: grouped row ->
 // token), every expert's two products, outputs added into the stream in the order of a token's choices (place:
 // (token, choice) -> grouped row).  xg, y, z: scratch [n_tokens * top, width | ff | width].
-extern "C" int idm_experts_grouped_step(const void* x, const int* src, const int* place, const int* counts, int n_experts,
+extern "C" int idm_experts_grouped_step(const void* x, const int* src, const int* place, const float* pair_w, const int* counts, int n_experts,
                                         const void* gate_up, long long gate_up_stride, const void* down, long long down_stride,
                                         void* xg, void* y, float* z, float* h, int n_tokens, int top, int width, int ff, int act,
                                         float weight, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
     if (idm_rows_gather(x, src, xg, n_tokens * top, width, stream)) return 1;
     if (idm_experts_grouped(xg, counts, n_experts, gate_up, gate_up_stride, down, down_stride, y, z, width, ff, act, stream)) return 1;
-    return idm_experts_combine(z, place, h, n_tokens, width, top, weight, stream);
+    return idm_experts_combine(z, place, pair_w, h, n_tokens, width, top, weight, stream);
 }
 
 // Single-token steps of many sequences, whose ids exist on the device only and whose shapes must not change from
@@ -369,8 +383,9 @@ extern "C" int idm_experts_grouped_step(const void* x, const int* src, const int
 // step has to do anyway is to stream every expert's matrices once: the products it does not need ride along), then
 // each token takes the outputs of its own experts.  z_all: [E, n_tokens, width] 32-bit; y: [n_tokens, ff] scratch.
 __global__ void __launch_bounds__(256) experts_pick_kernel(const float* __restrict__ z_all, const int* __restrict__ tokens,
-                                                           const int* __restrict__ table, float* __restrict__ h, int n_tokens,
-                                                           int width, int top, int n_experts, float weight) {
+                                                           const int* __restrict__ table, const float* __restrict__ pair_w,
+                                                           float* __restrict__ h, int n_tokens, int width, int top, int n_experts,
+                                                           float weight) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t t = blockIdx.x;
@@ -378,13 +393,16 @@ __global__ void __launch_bounds__(256) experts_pick_kernel(const float* __restri
         float s = 0.f;
         for (int k = 0; k < top; ++k) {
             const int e = table[(size_t)tokens[t] * top + k];
-            if (e >= 0 && e < n_experts) s += z_all[((size_t)e * n_tokens + t) * width + d];
+            if (e >= 0 && e < n_experts) {
+                const float z = z_all[((size_t)e * n_tokens + t) * width + d];
+                s = pair_w ? fmaf(pair_w[t * top + k], z, s) : s + z;
+            }
         }
         h[t * width + d] += s * weight;
     }
 }
 
-extern "C" int idm_experts_dense(const void* x, const int* tokens, const int* table, int n_experts, const void* gate_up,
+extern "C" int idm_experts_dense(const void* x, const int* tokens, const int* table, const float* pair_w, int n_experts, const void* gate_up,
                                  long long gate_up_stride, const void* down, long long down_stride, void* y, float* z_all,
                                  float* h, int n_tokens, int width, int ff, int top, int act, float weight, cudaStream_t stream) {
     if (n_tokens == 0) return 0;
@@ -393,7 +411,7 @@ extern "C" int idm_experts_dense(const void* x, const int* tokens, const int* ta
         if (idm_gemm_bf16_gated(x, (const T*)gate_up + (long long)e * gate_up_stride, y, n_tokens, ff, width, act, stream)) return 1;
         if (idm_gemm_bf16(y, (const T*)down + (long long)e * down_stride, z_all + (size_t)e * n_tokens * width, n_tokens, width, ff, stream)) return 1;
     }
-    idm_launch(experts_pick_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)z_all, tokens, table, h, n_tokens, width, top,
+    idm_launch(experts_pick_kernel, dim3(n_tokens), dim3(256), 0, stream, (const float*)z_all, tokens, table, pair_w, h, n_tokens, width, top,
                n_experts, weight);
     IDM_LAUNCH_CHECK("experts_pick");
     return 0;

@@ -1446,7 +1446,7 @@ extern "C" int idm_gemm_bf16_swiglu(const void* x, const void* w_tiled, void* y,
 // the same product with the gated activation chosen by number (gated_act in common.cuh): y = act(x . gate^T) * (x . up^T)
 extern "C" int idm_gemm_bf16_gated(const void* x, const void* w_tiled, void* y, int M, int inter, int K, int act,
                                    cudaStream_t stream) {
-    IDM_REQUIRE(act == 0 || act == 1, "gemm_gated: activation %d is not built", act);
+    IDM_REQUIRE(act >= 0 && act <= 2, "gemm_gated: activation %d is not built", act);
     GemmEpi e = {};
     e.y = (T*)y; e.inter = inter; e.act = act;
     const int tiles = (inter + 63) / 64;

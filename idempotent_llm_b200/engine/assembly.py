@@ -13,12 +13,14 @@ import torch
 
 from ..cache.spec import CacheNeed
 from ..config.specs import ModelSpec
-from ..parts.base import BLOCKS, MIXERS, NORMS, NormedDelta, Runtime
+from ..parts.base import BLOCKS, EMBEDDINGS, MIXERS, NORMS, CastStream, NormedDelta, Runtime
 from ..weights.loader import TensorDecl
 
 
 def declare_weights(spec: ModelSpec) -> List[TensorDecl]:
     decls = [TensorDecl(spec.embed_name, (spec.vocab_size, spec.hidden))]
+    if spec.embedding is not None:
+        decls += EMBEDDINGS.get(spec.embedding.kind).declare(spec.embedding, "")
     for layer in spec.layers:
         decls += BLOCKS.get(layer.kind).declare(layer)
     decls += NORMS.get(spec.final_norm.kind).declare(spec.final_norm, spec.final_norm_prefix)
@@ -38,9 +40,17 @@ def declare_weights(spec: ModelSpec) -> List[TensorDecl]:
     return unique
 
 
+EMBEDDING_CACHE_ID = -1     # the cache entry of what a token embedding keeps per sequence (mixers' entries count from 0)
+
+
 def cache_needs(spec: ModelSpec) -> Dict[int, CacheNeed]:
-    """cache id -> need, from the mixer of the schedule entry that writes it."""
+    """cache id -> need, from the mixer of the schedule entry that writes it (and from the token embedding, if it is
+    of a kind that keeps something per sequence)."""
     needs: Dict[int, CacheNeed] = {}
+    if spec.embedding is not None:
+        need = EMBEDDINGS.get(spec.embedding.kind).cache_need(spec.embedding)
+        if need is not None and need.state_shape is not None:
+            needs[EMBEDDING_CACHE_ID] = need
     for e in spec.schedule:
         need = MIXERS.get(spec.layers[e.layer].mixer.kind).cache_need(spec.layers[e.layer].mixer)
         if e.writes_cache:
@@ -59,6 +69,9 @@ class CausalLM:
             self.head = self.embed
         else:
             self.head = weights[spec.head_name].to(rt.dtype).contiguous()
+        self.embedding = None
+        if spec.embedding is not None:
+            self.embedding = EMBEDDINGS.get(spec.embedding.kind)(spec.embedding, weights, "", rt)
         self.blocks = [BLOCKS.get(layer.kind)(layer, weights, layer.prefix, rt) for layer in spec.layers]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, weights,
                                                           spec.final_norm_prefix, rt)
@@ -90,6 +103,8 @@ class CausalLM:
                 raise NotProgrammable("a scaled embedding is called from forward")
             if self.mix_in is not None or self.spec.logit_scale != 1.0 or self.spec.logit_softcap:
                 raise NotProgrammable("a stream mixed with the embedding, or scaled and capped logits, are called from forward")
+            if self.embedding is not None:
+                raise NotProgrammable("a token embedding with state is called from forward")
             prog = StepProgram(K)
             h = prog.buffer("stream", per_token=4 * hidden)
             prog.embed(self.embed, h)
@@ -117,14 +132,17 @@ class CausalLM:
             if prog is not None:
                 return prog.run(ctx, want_rows)
         scale = float(getattr(self.spec, "embed_scale", 1.0))
-        h = K.embed(ctx.tokens, self.embed) if scale == 1.0 else K.embed_scaled(ctx.tokens, self.embed, scale)
         pending = None
+        if self.embedding is not None:
+            h, pending = self.embedding.forward(self.embed, ctx, cache.state_of(EMBEDDING_CACHE_ID))
+        else:
+            h = K.embed(ctx.tokens, self.embed) if scale == 1.0 else K.embed_scaled(ctx.tokens, self.embed, scale)
         pad = {"pad": True} if self.spec.hidden % 8 else {}
         x0 = h.clone() if self.mix_in is not None else None         # the embedding output, kept for the mixes
         for e in self.spec.schedule:
             if e.mix_in:
                 # the stream (what is pending added first) and the embedding output side by side, times one matrix
-                if isinstance(pending, NormedDelta):
+                if isinstance(pending, (NormedDelta, CastStream)):
                     pending.add_into(h, K)
                     pending = None
                 h, pending = K.gemm_store(K.concat_cast(h, pending, x0), self.mix_in, **pad), None

@@ -35,9 +35,9 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]   # nev
 # the bfloat16 library the tensor-core kernels
 SOURCES: Dict[str, List[str]] = {
     "float32": ["runtime.cu", "elementwise.cu", "sampler.cu", "attention_generic.cu",
-                "attention_decode.cu", "short_conv.cu", "ssd_scan.cu", "head_finish.cu", "delta_rule.cu", "latent.cu", "experts.cu", "gemm_f32.cu"],
+                "attention_decode.cu", "short_conv.cu", "ssd_scan.cu", "head_finish.cu", "delta_rule.cu", "latent.cu", "experts.cu", "layer_norm.cu", "router.cu", "gemm_f32.cu"],
     "bfloat16": ["runtime.cu", "elementwise.cu", "sampler.cu", "attention_generic.cu",
-                 "attention_decode.cu", "short_conv.cu", "ssd_scan.cu", "head_finish.cu", "delta_rule.cu", "latent.cu", "experts.cu", "gemm_tcgen05.cu", "attention_tcgen05.cu",
+                 "attention_decode.cu", "short_conv.cu", "ssd_scan.cu", "head_finish.cu", "delta_rule.cu", "latent.cu", "experts.cu", "layer_norm.cu", "router.cu", "gemm_tcgen05.cu", "attention_tcgen05.cu",
                  "step_program.cu"],
 }
 DEFINES = {"float32": "-DIDM_F32", "bfloat16": "-DIDM_BF16"}

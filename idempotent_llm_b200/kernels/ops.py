@@ -69,13 +69,13 @@ SIGNATURES = {
     "idm_ssd_scan": (c_int, "piiiipiiippppqpippiiiiippipip"),
     "idm_ssd_group_norm": (c_int, "piipffpiiip"),
     "idm_attention_sink": (c_int, "ppiifpppippipppppiiiiifip"),
-    "idm_attention_biased": (c_int, "ppiifpppiipppiipppppiiiiifip"),
+    "idm_attention_biased": (c_int, "ppiifpppiipppiipppppiiiiififip"),
     "idm_head_finish": (c_int, "piiiipppppfipfiiiippppiipppip"),
     "idm_cols_cast": (c_int, "piiipiip"),
-    "idm_delta_prep": (c_int, "piiipiipiipppiiiip"),
+    "idm_delta_prep": (c_int, "piiipiipiiipppiiiip"),
     "idm_delta_scan": (c_int, "piiiipiippqpippiiiiiipp"),
     "idm_delta_scan_scratch_floats": (c_longlong, "iiii"),
-    "idm_delta_out": (c_int, "pipfpiifpiiiiip"),
+    "idm_delta_out": (c_int, "pipfpiiifpiiiiip"),
     "idm_add_rmsnorm2": (c_int, "ppiqppfpppiip"),
     "idm_gemm_bf16_gated": (c_int, "pppiiiip"),
     "idm_add_rmsnorm": (c_int, "ppiqpfppiip"),
@@ -107,14 +107,19 @@ SIGNATURES = {
     "idm_latent_attention_heads_per_block": (c_int, "iii"),
     "idm_latent_attention": (c_int, "pppippppppiiiifiip"),
     "idm_latent_expand_pack": (c_int, "pippiiiiiipifippppipppip"),
-    "idm_experts_few": (c_int, "ppppqqqpppiiiiiifp"),
-    "idm_experts_major": (c_int, "ppppqqqppppiiiiiifp"),
+    "idm_experts_few": (c_int, "pppppqqqpppiiiiiifp"),
+    "idm_experts_major": (c_int, "pppppqqqppppiiiiiifp"),
     "idm_rows_gather": (c_int, "pppiip"),
     "idm_experts_grouped": (c_int, "ppipqpqppiiip"),
-    "idm_experts_dense": (c_int, "pppipqpqpppiiiiifp"),
-    "idm_experts_grouped_step": (c_int, "ppppipqpqppppiiiiifp"),
+    "idm_experts_dense": (c_int, "ppppipqpqpppiiiiifp"),
+    "idm_experts_grouped_step": (c_int, "pppppipqpqppppiiiiifp"),
     "idm_dense_ff": (c_int, "ppppppiiiip"),
-    "idm_experts_combine": (c_int, "pppiiifp"),
+    "idm_experts_combine": (c_int, "ppppiiifp"),
+    "idm_route": (c_int, "pipppiiiiifp"),
+    "idm_experts_identity": (c_int, "ppppiiiip"),
+    "idm_post_layernorm": (c_int, "pppppfpiiip"),
+    "idm_add_layernorm": (c_int, "ppiqppfppiip"),
+    "idm_embed_bigram": (c_int, "ppppppppqppiiqqqp"),
     "idm_add_dyt": (c_int, "ppiqppfppiip"),
     "idm_act_cast": (c_int, "ppqip"),
     "idm_concat_cast": (c_int, "ppiqppiip"),
@@ -394,9 +399,11 @@ class Kernels:
             kv.n_kv_heads, dk, dv, scale, 0, self._stream()))
 
     def attention_biased(self, q, kv, ctx, scale: float, out, out_col: int, out_scale: float = 1.0, sink=None,
-                         slopes=None, gate=None, gate_stride: int = 0, gate_per_head: bool = False, window=None) -> None:
+                         slopes=None, gate=None, gate_stride: int = 0, gate_per_head: bool = False, window=None,
+                         softcap: float = 0.0, keep_first: int = 0) -> None:
         """The general attention kernel with all of its options: ``sink`` [n_q] joins the denominator, ``slopes`` [n_q]
-        times the distance to a key is taken off its score, ``window`` keys are seen, the result is multiplied by
+        times the distance to a key is taken off its score, ``window`` keys are seen (and, whatever the distance, the
+        sequence's first ``keep_first``), scores are capped at ``softcap * tanh(score / softcap)``, the result is multiplied by
         ``sigmoid(gate)`` (one number per head at ``gate[t, head]`` or one per channel) and by ``out_scale`` and
         stored at columns ``out_col ..`` of ``out``."""
         n, n_q, dk = q.shape
@@ -408,7 +415,7 @@ class Kernels:
             _p(q), _p(out), out.shape[1], out_col, float(out_scale), _p(kv.k), _p(kv.v), _p(kv.table), kv.table.shape[1],
             kv.ring, _p(sink), _p(slopes), _p(gate), gate_stride, 1 if gate_per_head else 0, _p(ctx.token_seq),
             _p(ctx.positions), _p(ctx.slots), _p(ctx.q_start), _p(ctx.cu_q), n, n_q, kv.n_kv_heads, dk, kv.v_head_dim,
-            float(scale), int(window) if window else 0, self._stream()))
+            float(scale), int(window) if window else 0, float(softcap or 0.0), int(keep_first or 0), self._stream()))
 
     def head_finish(self, proj, col_q: int, col_k: int, col_v, n_q: int, n_kv: int, dk: int, dv: int, biases, gammas,
                     eps: float, cs, mag: float, kv, ctx) -> torch.Tensor:
@@ -439,13 +446,14 @@ class Kernels:
         return out
 
     def delta_prep(self, c, c_q: int, c_k: int, a, a_col: int, proj, b_col: int, dt_bias, a_log, H: int, Hk: int,
-                   dk: int) -> torch.Tensor:
+                   dk: int, head_col: int = -1) -> torch.Tensor:
         """In place: q and k heads of ``c`` become unit vectors (q times ``dk ** -0.5``), columns ``a_col ..`` of ``a``
-        become decays; returns ``beta [N, H]``."""
+        become decays (``head_col`` >= 0: one decay per head from ``proj[:, head_col + h]``, written to all of the head's
+        columns of ``a``); returns ``beta [N, H]``."""
         n = c.shape[0]
         beta = torch.empty((n, H), dtype=torch.float32, device=self.device)
         self._check(self.lib.idm_delta_prep(_p(c), c.shape[1], c_q, c_k, _p(a), a.shape[1], a_col, _p(proj), proj.shape[1],
-                                            b_col, _p(dt_bias), _p(a_log), _p(beta), H, Hk, dk, n, self._stream()))
+                                            b_col, int(head_col), _p(dt_bias), _p(a_log), _p(beta), H, Hk, dk, n, self._stream()))
         return beta
 
     def delta_scan(self, c, c_q: int, c_k: int, c_v: int, g, g_col: int, beta, state, ctx, H: int, Hk: int, dk: int,
@@ -461,11 +469,13 @@ class Kernels:
                                             ctx.n_seqs, H, Hk, dk, dv, int(ctx.max_q_len), _p(scratch), self._stream()))
         return o
 
-    def delta_out(self, o, w, eps: float, gate, gate_col: int, scale: float, out, out_col: int, H: int, dv: int) -> None:
-        """``out[:, out_col ..] = rmsnorm over each head of o * w * sigmoid(gate columns) * scale``."""
+    def delta_out(self, o, w, eps: float, gate, gate_col: int, scale: float, out, out_col: int, H: int, dv: int,
+                  gate_act: int = 0) -> None:
+        """``out[:, out_col ..] = rmsnorm over each head of o * w * act(gate columns) * scale``; ``gate_act`` 0: sigmoid,
+        1: silu."""
         n = o.shape[0]
         self._check(self.lib.idm_delta_out(_p(o), o.shape[1], _p(w), float(eps), _p(gate), gate.shape[1], gate_col,
-                                           float(scale), _p(out), out.shape[1], out_col, n, H, dv, self._stream()))
+                                           int(gate_act), float(scale), _p(out), out.shape[1], out_col, n, H, dv, self._stream()))
 
     def add_rmsnorm2(self, h, delta, gamma1, gamma2, eps: float, post=None):
         """``h += delta`` in place, then both norms of the same row from one root mean square: returns ``(norm(h) *
@@ -1053,7 +1063,8 @@ class Kernels:
     # from this many (token, choice) pairs on, a step of few tokens walks its experts one by one
     EXPERT_MAJOR_FROM = 64
 
-    def experts_few(self, x, tokens, table, gate_up, row_stride: int, up_off: int, down, h, act: int, weight: float) -> None:
+    def experts_few(self, x, tokens, table, gate_up, row_stride: int, up_off: int, down, h, act: int, weight: float,
+                    pair_w=None) -> None:
         """``h[t] += weight * sum_k down[e] (act(gate[e] x_t) * up[e] x_t)``, ``e = table[tokens[t], k]``: every (token, choice)
         streams its expert's matrices (steps of few tokens).  ``gate_up [E, rows, width]`` holds an expert's gate and up
         rows: gate row f starts ``f * row_stride`` elements into the expert's block and its up row ``up_off`` behind it.
@@ -1072,12 +1083,13 @@ class Kernels:
         a = torch.empty((n, top, ff), dtype=torch.float32, device=self.device)
         if n * top > self.EXPERT_MAJOR_FROM and max(width, ff) * 32 + n * top * 4 <= 200 * 1024:
             # more pairs than a few: expert by expert, so that an expert's matrices are read once a step
-            z = torch.empty((n * top, width), dtype=torch.float32, device=self.device)
-            self._check(self.lib.idm_experts_major(_p(x), _p(tokens), _p(table), _p(gate_up), gate_up.shape[1] * width, row_stride,
+            # (zeros: a pair that names no expert of these has no block, and its row is added as it lies)
+            z = torch.zeros((n * top, width), dtype=torch.float32, device=self.device)
+            self._check(self.lib.idm_experts_major(_p(x), _p(tokens), _p(table), _p(pair_w), _p(gate_up), gate_up.shape[1] * width, row_stride,
                                                    up_off, _p(down), _p(a), _p(z), _p(h), n, width, ff, top, E, act, float(weight),
                                                    self._stream()), 3)
             return
-        self._check(self.lib.idm_experts_few(_p(x), _p(tokens), _p(table), _p(gate_up), gate_up.shape[1] * width, row_stride, up_off, _p(down),
+        self._check(self.lib.idm_experts_few(_p(x), _p(tokens), _p(table), _p(pair_w), _p(gate_up), gate_up.shape[1] * width, row_stride, up_off, _p(down),
                                              _p(a), _p(h), n, width, ff, top, E, act, float(weight), self._stream()), 2)
 
     def rows_gather(self, x, src) -> torch.Tensor:
@@ -1087,7 +1099,7 @@ class Kernels:
         self._check(self.lib.idm_rows_gather(_p(x), _p(src), _p(out), src.numel(), x.shape[1], self._stream()))
         return out
 
-    def experts_dense(self, x, tokens, table, gate_up, down, h, act: int, weight: float) -> None:
+    def experts_dense(self, x, tokens, table, gate_up, down, h, act: int, weight: float, pair_w=None) -> None:
         """``h[t] += weight * sum_k ff_e(x_t)``, ``e = table[tokens[t], k]``, by running EVERY expert over all the step's
         tokens with the library's matrix products and letting each token pick its own (single-token steps of many
         sequences: every expert's matrices are streamed once, in shapes that do not change from step to step)."""
@@ -1097,11 +1109,11 @@ class Kernels:
         E, _, ff = down.shape
         y = torch.empty((n, ff), dtype=self.dtype, device=self.device)
         z = torch.empty((E, n, width), dtype=torch.float32, device=self.device)
-        self._check(self.lib.idm_experts_dense(_p(x), _p(tokens), _p(table), E, _p(gate_up), gate_up.shape[1] * width, _p(down),
+        self._check(self.lib.idm_experts_dense(_p(x), _p(tokens), _p(table), _p(pair_w), E, _p(gate_up), gate_up.shape[1] * width, _p(down),
                                                width * ff, _p(y), _p(z), _p(h), n, width, ff, table.shape[1], act, float(weight),
                                                self._stream()), 2 * E + 1)
 
-    def experts_grouped_step(self, x, src, place, counts, gate_up, down, h, act: int, weight: float) -> None:
+    def experts_grouped_step(self, x, src, place, counts, gate_up, down, h, act: int, weight: float, pair_w=None) -> None:
         """A step's rows grouped by expert through every expert's gated feed-forward, from one call into the library:
         rows gathered in the order of their experts (``src [rows]``: grouped row -> token), the gated product (activation
         in its epilogue, ``gate_up`` in the layout of ``tile_gate_up``) and the down product of every expert that has
@@ -1116,7 +1128,7 @@ class Kernels:
         y = torch.empty((n * top, ff), dtype=self.dtype, device=self.device)
         z = torch.empty((n * top, width), dtype=torch.float32, device=self.device)
         with_rows = int((counts > 0).sum())
-        self._check(self.lib.idm_experts_grouped_step(_p(x), _p(src), _p(place), counts.ctypes.data, E, _p(gate_up),
+        self._check(self.lib.idm_experts_grouped_step(_p(x), _p(src), _p(place), _p(pair_w), counts.ctypes.data, E, _p(gate_up),
                                                       gate_up.shape[1] * width, _p(down), width * ff, _p(xg), _p(y), _p(z), _p(h),
                                                       n, top, width, ff, act, float(weight), self._stream()), 2 * with_rows + 2)
 
@@ -1132,12 +1144,78 @@ class Kernels:
         y = torch.empty((M, ff), dtype=self.dtype, device=self.device)
         self._check(self.lib.idm_dense_ff(_p(x), _p(w_up), _p(w_down), _p(z), _p(y), _p(h), M, Kd, ff, act, self._stream()), 3)
 
-    def experts_combine(self, z, place, h, weight: float) -> None:
-        """``h[t] += weight * sum_k z[place[t, k]]`` in ascending k (``place`` < 0: nothing)."""
+    def experts_combine(self, z, place, h, weight: float, pair_w=None) -> None:
+        """``h[t] += weight * sum_k pair_w[t, k] * z[place[t, k]]`` in ascending k (``place`` < 0: nothing; no ``pair_w``: 1)."""
         self._need(z, torch.float32, "experts output")
         self._need(place, torch.int32, "places")
         n, width = h.shape
-        self._check(self.lib.idm_experts_combine(_p(z), _p(place), _p(h), n, width, place.shape[1], float(weight), self._stream()))
+        self._check(self.lib.idm_experts_combine(_p(z), _p(place), _p(pair_w), _p(h), n, width, place.shape[1], float(weight), self._stream()))
+
+    def route(self, z, correction, top: int, groups: int, keep: int, scale: float):
+        """From 32-bit router logits ``z [N, E]`` to the experts each token uses: softmax over all E, choice by
+        ``softmax + correction`` among the experts of the ``keep`` best of ``groups`` equal groups of neighbours, the
+        ``top`` best in descending order; returns ``(chosen [N, top] int32, weight [N, top])`` with the weights the
+        chosen experts' softmax values over their sum, times ``scale``."""
+        self._need(z, torch.float32, "router logits")
+        n, E = z.shape
+        if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E):
+            raise KernelError(f"route: the correction must hold one 32-bit number for each of the {E} experts")
+        chosen = torch.empty((n, top), dtype=torch.int32, device=self.device)
+        weight = torch.empty((n, top), dtype=torch.float32, device=self.device)
+        self._check(self.lib.idm_route(_p(z), z.stride(0), _p(correction), _p(chosen), _p(weight), n, E, int(top), int(groups),
+                                       int(keep), float(scale), self._stream()))
+        return chosen, weight
+
+    def experts_identity(self, x, chosen, weight, h, n_real: int) -> None:
+        """``h[t] += x[t] * (the weights of t's pairs whose expert number is at least n_real)``: experts that hand
+        their input on."""
+        self._need(x, self.dtype, "experts input")
+        self._need(h, torch.float32, "residual stream")
+        n, width = x.shape
+        self._check(self.lib.idm_experts_identity(_p(x), _p(chosen), _p(weight), _p(h), n, width, chosen.shape[1], int(n_real),
+                                                  self._stream()))
+
+    def post_layernorm(self, h, y, w, b, scale, eps: float, cast: bool = False):
+        """``h += scale * layernorm(y)`` in place (``scale`` [hidden] or None); returns ``h`` in the storage dtype if
+        ``cast`` (what a sublayer without a norm in front of it reads), else None."""
+        self._need(h, torch.float32, "residual stream")
+        self._need(y, torch.float32, "sublayer output")
+        n, hidden = h.shape
+        if tuple(y.shape) != (n, hidden) or w.numel() != hidden or b.numel() != hidden or (scale is not None and scale.numel() != hidden):
+            raise KernelError(f"post_layernorm: stream {tuple(h.shape)}, output {tuple(y.shape)}, weight {w.numel()}")
+        x = torch.empty((n, hidden), dtype=self.dtype, device=self.device) if cast else None
+        self._check(self.lib.idm_post_layernorm(_p(h), _p(y), _p(w), _p(b), _p(scale), float(eps), _p(x), 2 if cast else 0, n,
+                                                hidden, self._stream()))
+        return x
+
+    def add_layernorm(self, h, delta, w, b, eps: float, rows=None) -> torch.Tensor:
+        """``h += delta`` in place (unless ``rows`` picks rows), then ``layernorm(h) * w + b`` in the storage dtype."""
+        self._need(h, torch.float32, "residual stream")
+        n, hidden = h.shape
+        dp, P, stride = self._delta_args(delta, n, hidden)
+        if rows is not None:
+            self._need(rows, torch.int32, "rows")
+        n_out = n if rows is None else rows.numel()
+        x = torch.empty((n_out, hidden), dtype=self.dtype, device=self.device)
+        self._check(self.lib.idm_add_layernorm(_p(h), dp, P, stride, _p(w), _p(b), float(eps), _p(x), _p(rows), n_out,
+                                               hidden, self._stream()))
+        return x
+
+    def embed_bigram(self, ctx, table, bigram, last, buckets: int, mul_prev: int, mul_cur: int, cast: bool = False):
+        """The 32-bit stream ``table[token] + bigram[row]`` with ``row = (previous token * mul_prev + token * mul_cur) %
+        buckets``, the table's last row for a sequence's first token; ``last [slots, 1]`` int32 holds every sequence's
+        last token between steps and is moved on.  Returns ``(h, h in the storage dtype or None)``."""
+        self._need(table, self.dtype, "embed table")
+        self._need(bigram, self.dtype, "bigram table")
+        if last.dtype != torch.int32 or last.dim() != 2 or bigram.shape[0] != buckets + 1 or bigram.shape[1] != table.shape[1]:
+            raise KernelError(f"embed_bigram: table {tuple(bigram.shape)} for {buckets} buckets, state {tuple(last.shape)} {last.dtype}")
+        n, hidden = ctx.tokens.numel(), table.shape[1]
+        h = torch.empty((n, hidden), dtype=torch.float32, device=self.device)
+        x = torch.empty((n, hidden), dtype=self.dtype, device=self.device) if cast else None
+        self._check(self.lib.idm_embed_bigram(_p(ctx.tokens), _p(ctx.token_seq), _p(ctx.positions), _p(ctx.cu_q), _p(ctx.slots),
+                                              _p(table), _p(bigram), _p(last), last.stride(0), _p(h), _p(x), n, hidden,
+                                              int(buckets), int(mul_prev), int(mul_cur), self._stream()))
+        return h, x
 
     def sample(self, logits: torch.Tensor, temperature: float, keys: Optional[torch.Tensor]) -> torch.Tensor:
         self._need(logits, torch.float32, "logits")

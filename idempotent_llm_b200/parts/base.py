@@ -21,6 +21,9 @@ Interfaces (duck-typed; the base classes document them):
 * ``FeedForward.forward(x, ctx) -> delta``.
 * ``PositionEncoding.tables(ctx)``: whatever its mixer kernels need for the
   step's tokens (computed once per step and shared between layers).
+* A token embedding other than the plain lookup (``EMBEDDINGS``): ``declare(spec, prefix)``,
+  ``cache_need(spec)`` (per-sequence state it keeps between steps, or None) and
+  ``forward(table, ctx, state) -> (h, pending)`` with ``h`` the 32-bit stream.
 * ``Block.forward(h, pending, ctx, kv, state, writes_cache) -> (h, pending)``:
   ``pending`` is a delta not yet added to ``h``; the next norm adds it.
 
@@ -78,6 +81,18 @@ class NormedDelta:
 
     def add_into(self, h, kernels) -> None:
         kernels.post_pre_norm(h, self.y, self.weight, self.eps)
+
+
+class CastStream:
+    """A pending "delta" that adds nothing: the stream is up to date, and ``x`` holds it in the storage dtype already
+    (written by the pass that last touched the stream).  A block whose first sublayer reads the stream itself takes
+    ``x`` instead of casting again; every other consumer treats it as no delta at all."""
+
+    def __init__(self, x):
+        self.x = x
+
+    def add_into(self, h, kernels) -> None:
+        return None
 
 
 class Part:
@@ -148,6 +163,7 @@ class _Registry:
 
 
 NORMS = _Registry("norm")
+EMBEDDINGS = _Registry("token embedding")
 POSITIONS = _Registry("position encoding")
 MIXERS = _Registry("mixer")
 FEED_FORWARDS = _Registry("feed-forward")

@@ -5,8 +5,11 @@ In this file's notation, for the mixer's input h of one sequence (positions t = 
     q, k, v  = Wq h (+ bq), Wk h (+ bk), Wv h (+ bv)     or, with ``values_from_keys``, v = k at this point and no Wv
     q, k    <- norm(q), norm(k)                          per head: x / sqrt(mean(x^2) + eps) * w, one w for all heads
     q, k    <- turn(q), turn(k)                          the first ``position.dim`` dims of each head, by position
-    s_tj     = scale * q_t . k_j - slope_i (t - j)       for t - window < j <= t;  slope_i = 2^(-c (i + 1) / heads)
-    a_tj     = exp(s_tj) / (sum_j' exp(s_tj') [+ 1])     the added 1 is a sink of score 0 without a value
+    s_tj     = scale * q_t . k_j                         for t - window < j <= t, and with ``keep_first`` also for j < keep_first
+    s_tj    <- cap * tanh(s_tj / cap)                    with ``softcap``
+    s_tj    <- s_tj - slope_i (t - j)                    with slopes;  slope_i = 2^(-c (i + 1) / heads)
+    a_tj     = exp(s_tj) / (sum_j' exp(s_tj') [+ exp(z_i)])   the added term is a sink without a value: z_i = 0
+                                                         (``unit_sink``) or a learned number per head (``sink``)
     o_t      = (sum_j a_tj v_j) [* sigmoid(Wg h_t)_i]    one gate number per head
     out      = Wo o (+ bo)
 
@@ -44,6 +47,8 @@ class HeadAttention(Mixer):
                   TensorDecl(prefix + nm.k_norm, (s.key_dim,), init="one_plus_normal")]
         if s.head_gate:
             d.append(TensorDecl(prefix + nm.gate, (s.n_heads, s.hidden)))
+        if s.sink:
+            d.append(TensorDecl(prefix + nm.sink, (s.n_heads,), init="unit_normal"))
         d.append(TensorDecl(prefix + nm.o, (s.hidden, s.n_heads * s.value_dim)))
         if s.bias_out:
             d.append(TensorDecl(prefix + nm.o + nm.bias, (s.hidden,)))
@@ -61,6 +66,10 @@ class HeadAttention(Mixer):
             raise ValueError("n_heads must be a multiple of n_kv_heads")
         if s.values_from_keys and s.value_dim != s.key_dim:
             raise ValueError("keys that double as values have the values' size")
+        if s.sink and s.unit_sink:
+            raise ValueError("a softmax has one sink: a learned one or the one of score 0")
+        if s.keep_first < 0 or (s.softcap is not None and not s.softcap > 0):
+            raise ValueError(f"normed attention: keep_first={s.keep_first}, softcap={s.softcap}")
         self.spec, self.rt = spec, rt
         f32 = lambda n: weights[prefix + n].to(torch.float32).contiguous()
         names = [nm.q, nm.k] + ([] if s.values_from_keys else [nm.v])
@@ -77,6 +86,10 @@ class HeadAttention(Mixer):
             self.biases += (None,)
         self.gammas = (f32(nm.q_norm), f32(nm.k_norm)) if s.qk_norm else (None, None)
         self.sink = torch.zeros(s.n_heads, dtype=torch.float32, device=rt.device) if s.unit_sink else None
+        if s.sink:
+            self.sink = f32(nm.sink)
+        self.keep_first = int(s.keep_first) if s.window else 0      # (without a window every key is seen anyway)
+        self.softcap = float(s.softcap) if s.softcap else 0.0
         self.slopes = None
         if s.slope_exponent is not None:
             h = torch.arange(1, s.n_heads + 1, dtype=torch.float64)
@@ -99,13 +112,14 @@ class HeadAttention(Mixer):
                           s.n_heads, s.n_kv_heads, s.key_dim, s.value_dim, self.biases, self.gammas, s.eps, cs,
                           self.magnitude, kv, ctx)
         gate = proj[:, col0 + self.col_gate:] if s.head_gate else None
-        if K.attention_tc_fits(kv, s.key_dim, s.value_dim) and s.softmax_scale > 0:
+        if K.attention_tc_fits(kv, s.key_dim, s.value_dim) and s.softmax_scale > 0 and not self.keep_first and not self.softcap:
             # on the tensor cores, for prompts and single tokens alike; gate and constant in a pass of their own
             o = K.attention_tc(q, kv, ctx, s.softmax_scale, sink=self.sink, slopes=self.slopes, window=s.window)
             K.gate_scale(o, gate, proj.shape[1], out_scale, out, out_col, gate_group=s.value_dim)
         else:
             K.attention_biased(q, kv, ctx, s.softmax_scale, out, out_col, out_scale, sink=self.sink, slopes=self.slopes,
-                               gate=gate, gate_stride=proj.shape[1], gate_per_head=True, window=s.window)
+                               gate=gate, gate_stride=proj.shape[1], gate_per_head=True, window=s.window,
+                               softcap=self.softcap, keep_first=self.keep_first)
 
     def forward(self, x, ctx, kv, state, writes_cache: bool, residual=None):
         """Returns the delta ``[1, N, hidden]``, or None after adding it into ``residual`` in place."""

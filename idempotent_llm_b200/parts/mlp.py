@@ -12,7 +12,7 @@ from .base import FEED_FORWARDS, FeedForward
 
 
 # the kernels' numbers of the gated activations (csrc/common.cuh: gated_act)
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu": 2}
 
 
 @FEED_FORWARDS.register("gated_mlp")

@@ -79,6 +79,8 @@ def _register_builtin() -> None:
     register_architecture(PANODRA, PanodraConfig)
     from .config.fuginex import ARCHITECTURE as FUGINEX, FuginexConfig
     register_architecture(FUGINEX, FuginexConfig)
+    from .config.pununex import ARCHITECTURE as PUNUNEX, PununexConfig
+    register_architecture(PUNUNEX, PununexConfig)
 
 
 _register_builtin()
