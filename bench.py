@@ -270,6 +270,41 @@ def fuginex_prefill_flops(cfg, lens) -> float:
     return total + 2 * W * cfg.vocab * len(lens)
 
 
+def pununex_prefill_flops(cfg, lens) -> float:
+    """The same count for a Pununex configuration, per layer: the mixer's input and output projections (both sides of a
+    parallel layer, with the low-rank pairs at the presets' 64), attention over the keys a query sees (the window and
+    the kept first keys), the delta rules, and the feed-forward a token uses (dense: three matrices; routed: the
+    router, `top` experts less the expected share of identity experts, and the shared expert)."""
+    W, tokens, total = cfg.width, sum(lens), 0.0
+
+    def seen(t, window, keep):
+        if window is None or window >= t:
+            return t * (t + 1) // 2
+        return window * (window + 1) // 2 + (t - window) * window + sum(min(keep, max(0, p - window + 1)) for p in range(window, t))
+
+    def delta(r, per_head):
+        lin = W * (2 * r.kv_heads * r.dim + r.heads * r.vdim + r.heads) + r.heads * r.vdim * W
+        lin += W * (r.heads + r.heads * r.vdim) if per_head else W * 128 + 64 * r.heads * r.dim + 64 * r.heads * r.vdim
+        return lin, 8 * tokens * r.heads * r.dim * r.vdim
+    for L in cfg.layers:
+        linear = 0
+        if L.mlp is not None and L.mlp.kind == "dense":
+            linear += 3 * W * L.mlp.ff
+        elif L.mlp is not None:
+            r = L.mlp.router
+            total_e = r.experts + r.identity
+            linear += W * total_e + 3 * W * L.mlp.ff * r.top * r.experts / total_e + 3 * W * (L.mlp.shared_ff or 0)
+        if L.type == "delta":
+            lin, rec = delta(L.delta, True)
+        else:
+            l = L.left
+            lin, rec = delta(L.right, False)
+            lin += W * (l.heads * l.dim + l.kv_heads * (l.dim + l.vdim)) + l.heads * l.vdim * W
+            total += sum(l.heads * 2 * (l.dim + l.vdim) * seen(t, l.window, l.keep_first) for t in lens)
+        total += 2 * tokens * (linear + lin) + rec
+    return total + 2 * W * cfg.vocab * len(lens)
+
+
 def panodra_prefill_flops(cfg, lens) -> float:
     """The same count for a Panodra configuration, per layer run: the joint input projection, every head's keys and
     values from the latent, the output projection, causal attention per head over keys of dim + rot_dim and values of
@@ -311,6 +346,8 @@ def prefill_flops(cfg, lens) -> float:
         return panodra_prefill_flops(cfg, lens)
     if getattr(cfg, "architecture", "") == "Fuginex":
         return fuginex_prefill_flops(cfg, lens)
+    if getattr(cfg, "architecture", "") == "Pununex":
+        return pununex_prefill_flops(cfg, lens)
     if hasattr(cfg, "layers") and not hasattr(cfg, "hidden_size"):
         return lunulix_prefill_flops(cfg, lens)
     H, L, V = cfg.hidden_size, cfg.num_hidden_layers, cfg.vocab_size
@@ -479,7 +516,8 @@ def decode_kernel_times(lm, lens, seed: int):
              "gemm_gated", "gemm_qkv", "attention_tc", "attention_generic", "attention_sink", "conv_qkv_cache", "short_conv",
              "ssd_scan", "ssd_group_norm", "token_gate", "gated_act", "attention_lse_gate", "add_dyt", "latent_kv_finish",
              "headwise", "latent_attention", "experts_few", "act_cast", "concat_cast", "logit_cap", "add_rmsnorm2", "head_finish",
-             "attention_biased", "cols_cast", "delta_prep", "delta_scan", "delta_out", "gate_scale"]
+             "attention_biased", "cols_cast", "delta_prep", "delta_scan", "delta_out", "gate_scale", "embed_bigram", "post_layernorm",
+             "add_layernorm", "route", "experts_identity", "experts_dense", "experts_grouped_step", "conv_state_update"]
     names = [n for n in names if hasattr(K, n)]
     out, saved = {}, {n: getattr(K, n) for n in names}
     timing = [False]
@@ -514,9 +552,13 @@ def decode_kernel_times(lm, lens, seed: int):
     return {n: {"calls": c, "ms": round(ms, 4)} for n, (c, ms) in sorted(out.items(), key=lambda kv: -kv[1][1])}
 
 
+BESIDE = {"fuginex": "lunulix", "pununex": "fuginex"}      # a design's closest other one (default: qwen3)
+
+
 def design_comparison(args) -> int:
-    """``--design lunulix`` / ``--design panodra`` / ``--design fuginex``: decode and prefill throughput of that design
-    beside the closest other one (Qwen3; for Fuginex, Lunulix: an attention and a recurrence side by side) at equal width,
+    """``--design lunulix`` / ``--design panodra`` / ``--design fuginex`` / ``--design pununex``: decode and prefill
+    throughput of that design beside the closest other one (Qwen3; for Fuginex, Lunulix: an attention and a recurrence
+    side by side; for Pununex, Fuginex: a windowed attention beside a delta rule) at equal width,
     depth (layer runs), heads, feed-forward size and vocabulary (random weights), with where a step's time goes kernel by
     kernel."""
     import torch
@@ -530,7 +572,7 @@ def design_comparison(args) -> int:
     sampler = ClockSampler()
     sampler.start()
     for size in sizes:
-        for arch in ({"fuginex": "lunulix"}.get(args.design, "qwen3"), args.design):
+        for arch in (BESIDE.get(args.design, "qwen3"), args.design):
             cfg = preset(f"{arch}-{size}")
             lm = idm.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=64 * 2304, max_seqs=64, max_seq_len=2304)
             r = {"params_b": lm.model.weight_bytes() / 2e9}
@@ -547,7 +589,7 @@ def design_comparison(args) -> int:
             rows[f"{arch}-{size}"] = r
             del lm
             torch.cuda.empty_cache()
-    beside = {"fuginex": "lunulix"}.get(args.design, "qwen3")
+    beside = BESIDE.get(args.design, "qwen3")
     print(json.dumps({"metric": f"decode and prefill of {args.design} beside {beside} at equal sizes (bf16, random weights)",
                       "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": max(args.warmup, 3), "dtype": "bf16",
                       "data": "synthetic: seeded random weights and uniform-random token ids", "peaks": pk,
@@ -577,7 +619,7 @@ def main() -> int:
     ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps; the median counts")
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64 and the 32-bit check")
     ap.add_argument("--skip-sizes", action="store_true", help="leave out the points at 8B and 32B layer sizes")
-    ap.add_argument("--design", default="", choices=["", "lunulix", "panodra", "fuginex"],
+    ap.add_argument("--design", default="", choices=["", "lunulix", "panodra", "fuginex", "pununex"],
                     help="instead of the default workload: this design beside its closest other one at equal layer sizes")
     ap.add_argument("--design-sizes", default="0.6b,8b", help="layer sizes of --design (presets <design>-<size>)")
     args = ap.parse_args()

@@ -74,6 +74,9 @@ struct AttnTcArgs {
                                                        // the softmax's sum with no key and no value
     const float* slopes;                               // [n_q] or null: slopes[head] * (p - j) is taken off the scaled score of key j
     int window;                                        // > 0: a query at p sees keys p - window + 1 .. p; 0: every earlier key
+    int keep_first;                                    // > 0 (with a window): keys j < keep_first are seen from any distance
+    float cap_in, cap_out;                             // cap_in > 0: a raw score s becomes cap_out * tanh(s * cap_in), which is
+                                                       // (cap / scale) tanh(s scale / cap): the cap on the scaled score, in raw units
     const int* tile_seq; const int* tile_start;
     const int* cu_q; const int* q_start; const int* kv_len; const int* slots;
     const int* table; int table_stride;
@@ -316,17 +319,33 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int R = a.run_blocks;
     // With a window, the runs that lie wholly before the first key the tile's first row sees are left out: runs keep
     // their absolute places, and from here on they are counted from the first one that is walked.
+    //
+    // Kept first keys (keep_first, with a window) lie in key blocks 0 .. kb-1.  If those end before the window's first
+    // run, the walk is: the kept blocks (runs of their own at their absolute places, the last one cut short behind
+    // the last kept key), then on from the window's first run.  The blocks of a tile are numbered in the order of
+    // that walk (w = 0, 1, ..): block_of(w) is a block's place among the sequence's keys, run_of(w) its run counted
+    // in walk order, walk_of(run) a run's first block.  A run starts wherever block_of(w) is a multiple of R, which
+    // the first block behind the gap is too.
     const int W = a.window;
-    const int run_lo = W > 0 ? (max(0, p_first - W + 1) / AP_BN) / R : 0;
-    const int n_runs = (nb_tile + R - 1) / R - run_lo;
+    const int win_run = W > 0 ? (max(0, p_first - W + 1) / AP_BN) / R : 0;
+    const int kb = (W > 0 && a.keep_first > 0) ? (min(a.keep_first, p_last + 1) + AP_BN - 1) / AP_BN : 0;
+    const bool gap = kb > 0 && kb < win_run * R;                 // (kept blocks that reach the window's first run: one walk from 0)
+    const int run_lo = (kb > 0 && !gap) ? 0 : win_run;           // the first run walked behind the kept blocks' own
+    const int skip_at = gap ? kb : 0, skip_by = run_lo * R - skip_at;
+    const int kept_runs = gap ? (kb + R - 1) / R : 0;
+    auto block_of = [&](int w) { return w < skip_at ? w : w + skip_by; };
+    auto run_of = [&](int w) { return w < skip_at ? w / R : (w + skip_by) / R - run_lo + kept_runs; };
+    const int nb_walk = nb_tile - skip_by;                       // key blocks of the tile's walk
+    const int n_runs = kept_runs + (nb_tile + R - 1) / R - run_lo;
+    auto walk_of = [&](int rn) { return rn >= n_runs ? nb_walk : rn < kept_runs ? rn * R : skip_at + (rn - kept_runs) * R; };
     if (through_scratch && run >= n_runs) return;                // (the whole block, before anything is set up)
     const int pool_at = parted ? a.tile_pool[tile] : -1;
     const int n_parts = pool_at >= 0 ? (n_runs + a.runs_per_part - 1) / a.runs_per_part : 1;
     if (part >= n_parts) return;
     const bool shared = n_parts > 1;                             // this tile's runs go through the pool, several blocks walk them
-    // this block's key blocks b_first .. b_first + nb - 1
-    const int b_first = (run_lo + (through_scratch ? run : shared ? part * a.runs_per_part : 0)) * R;
-    const int nb = through_scratch ? min(R, nb_tile - b_first) : shared ? min(a.runs_per_part * R, nb_tile - b_first) : nb_tile - b_first;
+    // this block's key blocks, in walk order: b_first .. b_first + nb - 1
+    const int b_first = walk_of(through_scratch ? run : shared ? part * a.runs_per_part : 0);
+    const int nb = (through_scratch ? walk_of(run + 1) : shared ? walk_of((part + 1) * a.runs_per_part) : nb_walk) - b_first;
     const int n_hg = a.n_q >> gs;
 
     if (threadIdx.x == 0) {
@@ -360,10 +379,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (int h = 0; h < HT; ++h)
                 tma_load_3d(base + S::Q_OFF + h * AP_BM * 128, &map_q, h * 64, head0, tok0, q_full);
         }
-        const int* pages = a.table + (size_t)a.slots[seq] * a.table_stride + b_first;
+        const int* pages = a.table + (size_t)a.slots[seq] * a.table_stride;
         int my_page = 0;
         for (int b = 0; b < nb; ++b) {
-            if ((b & 31) == 0) my_page = b + lane < nb ? pages[b + lane] : 0;
+            if ((b & 31) == 0) my_page = b + lane < nb ? pages[block_of(b_first + b + lane)] : 0;
             const int page = __shfl_sync(0xffffffffu, my_page, b & 31);
             const int row = (page * a.n_kv + g) * IDM_PAGE;
             const int vb = b & 1;                                // this block's key and value buffers
@@ -417,7 +436,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t vbase = base + S::V_OFF + (b & 1) * S::V_BYTES;
-                const bool fresh = (b_first + b) % R == 0;       // a run's first block starts its context from nothing
+                const bool fresh = block_of(b_first + b) % R == 0;   // a run's first block starts its context from nothing
 #pragma unroll
                 for (int kk = 0; kk < AP_BN / 16; ++kk) {        // O (+)= P . V_b
                     const uint64_t ad = umma_desc_kmajor(base + S::P_OFF) + 2 * kk;
@@ -476,7 +495,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (!ok) break;
             if (threadIdx.x == 0) attn_stamp(2 + 2 * b);         // scores of block b are there
             tc_fence_after();
-            const bool run_start = b > 0 && (b_first + b) % R == 0;
+            const bool run_start = b > 0 && block_of(b_first + b) % R == 0;
             float m_prev = 0.f, l_prev = 0.f;
             if (run_start) { m_prev = m_ref; l_prev = l; m_ref = -INFINITY; l = 0.f; }
             uint32_t sr[AP_BN];
@@ -488,10 +507,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_empty(b & 1));
-            const int key0 = (b_first + b) * AP_BN;               // position of the block's first key
+            const int key0 = block_of(b_first + b) * AP_BN;       // position of the block's first key
             float alpha = 1.f, row_sum = 0.f;
             uint32_t packed[AP_BN / 2];
             if (row_live) {
+                if (a.cap_in > 0.f) {                             // the cap, before any key is masked (tanh of -inf is -1)
+#pragma unroll
+                    for (int j = 0; j < AP_BN; ++j) {
+                        float th;
+                        asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(__fmul_rn(__uint_as_float(sr[j]), a.cap_in)));
+                        sr[j] = __float_as_uint(__fmul_rn(th, a.cap_out));
+                    }
+                }
                 const bool diagonal = key0 + AP_BN - 1 > p_first; // some key of the block lies past row 0's position
                 if (diagonal) {
 #pragma unroll
@@ -501,7 +528,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (W > 0 && key0 + W <= p_r) {                   // some key of the block lies before the row's window
 #pragma unroll
                     for (int j = 0; j < AP_BN; ++j)
-                        if (key0 + j + W <= p_r) sr[j] = 0xff800000u;
+                        if (key0 + j + W <= p_r && key0 + j >= a.keep_first) sr[j] = 0xff800000u;
                 }
                 if (a.slopes) {
                     const float d0 = (float)(key0 - p_r);
@@ -548,13 +575,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (run_start && shared) {
                     // the run before this block is complete: its result goes to its slot (the MMA that starts the
                     // new run's context overwrites O only after this warp's arrival below)
-                    if (warp_live) leave_run((b_first + b) / R - 1 - run_lo, m_prev, l_prev);
+                    if (warp_live) leave_run(run_of(b_first + b) - 1, m_prev, l_prev);
                 } else if (run_start) {
                     // the run before this block is complete: fold it into the row's context so far (the MMA
                     // that starts the new run's context overwrites O only after this warp's arrival below)
                     if (warp_live) {
                         float a_, b_;
-                        const bool first = (b_first + b) == (run_lo + 1) * R;   // it was the tile's first run: nothing to add to
+                        const bool first = run_of(b_first + b) == 1;       // it was the tile's first run: nothing to add to
                         fold_coeffs(M_tot, L_tot, m_prev, l_prev, a_, b_);
                         float4* mine = reinterpret_cast<float4*>(tot);
 #pragma unroll 1
@@ -630,7 +657,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // nobody waits for anybody for ever.)
             if (ok && warp_live) {
                 tc_fence_after();
-                leave_run(through_scratch ? run : (b_first + nb - 1) / R - run_lo, m_ref, l);
+                leave_run(through_scratch ? run : run_of(b_first + nb - 1), m_ref, l);
                 __threadfence();
             }
             count_and_fold_runs<HD>(a, part0, part_floats, n_runs, through_scratch ? n_runs : n_parts, rows_valid, tok0, head0,
@@ -718,7 +745,8 @@ extern "C" long long idm_attention_tc_scratch_floats(int n_tiles, int n_q, int n
 // 128 / heads_per_tile tokens, longest first; rows_cap: the most rows (tokens x heads_per_tile) any tile has.  max_runs > 0: every run of `run_blocks` key blocks is a
 // block of its own and results meet in scratch; max_runs == 0:
 // one block per tile and head group (`scratch` may be null if no tile has more than run_blocks key blocks).
-static int attention_tc_any(const void* q, void* out, const float* sink, const float* slopes, int window, const void* k_pool, const void* v_pool, int n_pages,
+static int attention_tc_any(const void* q, void* out, const float* sink, const float* slopes, int window, float softcap, int keep_first,
+                            const void* k_pool, const void* v_pool, int n_pages,
                             const int* table, int table_stride, const int* tile_seq, const int* tile_start,
                             int n_tiles, const int* cu_q, const int* q_start, const int* kv_len,
                             const int* slots, int n_tokens, int n_q, int n_kv, int hd, float scale,
@@ -758,7 +786,10 @@ static int attention_tc_any(const void* q, void* out, const float* sink, const f
         IDM_REQUIRE(r == 0, "attention_tc: tensor map for v failed (%d)", r);
     }
     AttnTcArgs a;
-    a.out = (T*)out; a.sink = sink; a.slopes = slopes; a.window = window > 0 ? window : 0; a.tile_seq = tile_seq; a.tile_start = tile_start; a.cu_q = cu_q; a.q_start = q_start;
+    a.out = (T*)out; a.sink = sink; a.slopes = slopes; a.window = window > 0 ? window : 0;
+    a.keep_first = (window > 0 && keep_first > 0) ? keep_first : 0;
+    a.cap_in = softcap > 0.f ? scale / softcap : 0.f; a.cap_out = softcap > 0.f ? softcap / scale : 0.f;
+    a.tile_seq = tile_seq; a.tile_start = tile_start; a.cu_q = cu_q; a.q_start = q_start;
     a.kv_len = kv_len; a.slots = slots; a.table = table; a.table_stride = table_stride;
     a.n_q = n_q; a.n_kv = n_kv; a.gp_shift = gs; a.scale_log2 = scale * 1.4426950408889634f;
     a.run_blocks = run_blocks; a.max_runs = max_runs; a.rows_cap = rows_cap;
@@ -767,8 +798,8 @@ static int attention_tc_any(const void* q, void* out, const float* sink, const f
     a.pool = a.parts ? a.parts + groups * (long long)(AP_BM * hd) : nullptr;
     IDM_REQUIRE(a.max_parts == 0 || (scratch != nullptr && runs_per_part >= 1 && groups <= AP_COUNTERS),
                 "attention_tc: shared tiles need scratch, runs_per_part >= 1 and at most %d tiles x head groups (got %lld)", AP_COUNTERS, groups);
-    // (the kernel for few rows has neither windows nor slopes: such layers' single tokens take the general one, a block a run)
-    if (g_attn_few_rows && slopes == nullptr && window <= 0 && attention_few_rows_can(hd, rows_cap, run_blocks, max_runs, groups))
+    // (the kernel for few rows has neither windows nor slopes nor a cap: such layers' single tokens take the general one, a block a run)
+    if (g_attn_few_rows && slopes == nullptr && window <= 0 && !(softcap > 0.f) && attention_few_rows_can(hd, rows_cap, run_blocks, max_runs, groups))
         return hd == 64 ? launch_attention_few_rows<64>(mk, mv, a, (const T*)q, n_tiles, stream)
                         : launch_attention_few_rows<128>(mk, mv, a, (const T*)q, n_tiles, stream);
     return hd == 64 ? launch_attention_tc<64>(mq, mk, mv, a, n_tiles, stream)
@@ -781,7 +812,7 @@ extern "C" int idm_attention_tc(const void* q, void* out, const void* k_pool, co
                                 const int* slots, int n_tokens, int n_q, int n_kv, int hd, float scale,
                                 int run_blocks, int max_runs, int rows_cap, float* scratch, const int* tile_pool,
                                 int max_parts, int runs_per_part, cudaStream_t stream) {
-    return attention_tc_any(q, out, nullptr, nullptr, 0, k_pool, v_pool, n_pages, table, table_stride, tile_seq, tile_start, n_tiles, cu_q,
+    return attention_tc_any(q, out, nullptr, nullptr, 0, 0.f, 0, k_pool, v_pool, n_pages, table, table_stride, tile_seq, tile_start, n_tiles, cu_q,
                             q_start, kv_len, slots, n_tokens, n_q, n_kv, hd, scale, run_blocks, max_runs, rows_cap, scratch,
                             tile_pool, max_parts, runs_per_part, stream);
 }
@@ -794,23 +825,26 @@ extern "C" int idm_attention_tc_sink(const void* q, void* out, const float* sink
                                      const int* kv_len, const int* slots, int n_tokens, int n_q, int n_kv, int hd,
                                      float scale, int run_blocks, int max_runs, int rows_cap, float* scratch,
                                      const int* tile_pool, int max_parts, int runs_per_part, cudaStream_t stream) {
-    return attention_tc_any(q, out, sink, nullptr, 0, k_pool, v_pool, n_pages, table, table_stride, tile_seq, tile_start, n_tiles, cu_q,
+    return attention_tc_any(q, out, sink, nullptr, 0, 0.f, 0, k_pool, v_pool, n_pages, table, table_stride, tile_seq, tile_start, n_tiles, cu_q,
                             q_start, kv_len, slots, n_tokens, n_q, n_kv, hd, scale, run_blocks, max_runs, rows_cap, scratch,
                             tile_pool, max_parts, runs_per_part, stream);
 }
 
 // The same attention with every option: a sink per q-head (or null), a slope per q-head (or null: slopes[head] times
 // the distance to a key is taken off its scaled score), a window (> 0: a query sees itself and the window - 1 keys
-// before it; the cache keeps every key, runs of key blocks that no row of a tile sees are not walked).
+// before it; the cache keeps every key, runs of key blocks that no row of a tile sees are not walked), first keys that
+// stay seen behind the window (keep_first), and a cap on the scaled scores (softcap > 0: cap * tanh(score / cap), by
+// the hardware's tanh, whose error is below the rounding of the softmax's weights to bfloat16).
 extern "C" int idm_attention_tc_biased(const void* q, void* out, const float* sink, const float* slopes, int window,
-                                       const void* k_pool, const void* v_pool, int n_pages, const int* table,
+                                       float softcap, int keep_first, const void* k_pool, const void* v_pool, int n_pages, const int* table,
                                        int table_stride, const int* tile_seq, const int* tile_start, int n_tiles,
                                        const int* cu_q, const int* q_start, const int* kv_len, const int* slots,
                                        int n_tokens, int n_q, int n_kv, int hd, float scale, int run_blocks, int max_runs,
                                        int rows_cap, float* scratch, const int* tile_pool, int max_parts,
                                        int runs_per_part, cudaStream_t stream) {
     IDM_REQUIRE(scale > 0.f, "attention_tc: the scale of the scores must be positive, not %g", (double)scale);
-    return attention_tc_any(q, out, sink, slopes, window, k_pool, v_pool, n_pages, table, table_stride, tile_seq, tile_start,
+    IDM_REQUIRE(keep_first >= 0 && softcap >= 0.f, "attention_tc: keep_first=%d softcap=%g", keep_first, (double)softcap);
+    return attention_tc_any(q, out, sink, slopes, window, softcap, keep_first, k_pool, v_pool, n_pages, table, table_stride, tile_seq, tile_start,
                             n_tiles, cu_q, q_start, kv_len, slots, n_tokens, n_q, n_kv, hd, scale, run_blocks, max_runs,
                             rows_cap, scratch, tile_pool, max_parts, runs_per_part, stream);
 }

@@ -97,7 +97,7 @@ SIGNATURES = {
     "idm_attention_tc_scratch_floats": (c_longlong, "iiiiii"),
     "idm_attention_tc": (c_int, "ppppipippippppiiiifiiippiip"),
     "idm_attention_tc_sink": (c_int, "pppppipippippppiiiifiiippiip"),
-    "idm_attention_tc_biased": (c_int, "ppppippipippippppiiiifiiippiip"),
+    "idm_attention_tc_biased": (c_int, "ppppifippipippippppiiiifiiippiip"),
     "idm_gate_scale": (c_int, "ppiifpiiiip"),
     "idm_attention_tc_status": (c_int, ""),
     "idm_attention_tc_set_few_rows": (c_int, "i"),
@@ -602,7 +602,7 @@ class Kernels:
         return self.attention_generic(q, kv, ctx, k_new, v_new, scale, window)
 
     def attention_tc(self, q, kv, ctx, scale: float, out=None, through_scratch=None, share=None, sink=None, slopes=None,
-                     window=None) -> torch.Tensor:
+                     window=None, softcap: float = 0.0, keep_first: int = 0) -> torch.Tensor:
         """Causal attention on the tensor cores: tiles of (128 / gp tokens) x (gp q-heads of one kv-head).
 
         Steps with few tokens per sequence (at most 32 rows a tile: single tokens above all) give every
@@ -620,13 +620,14 @@ class Kernels:
                 _p(ctx.kv_len), _p(ctx.slots), n, n_q, kv.n_kv_heads,
                 hd, scale, self.attention_run_blocks, max_runs, rows_cap, scratch, tile_pool, max_parts, per,
                 self._stream())
-        if slopes is not None or window:
+        if slopes is not None or window or softcap:
             # a slope per q-head times the distance to a key off its score, and a window of keys a query sees (runs of
             # key blocks before every window of a tile are not walked)
             for name, t in (("sink", sink), ("slopes", slopes)):
                 if t is not None and (t.dtype != torch.float32 or t.numel() != n_q):
                     raise KernelError(f"attention: {name} must hold one 32-bit number per head")
-            self._check(self.lib.idm_attention_tc_biased(_p(q), _p(out), _p(sink), _p(slopes), int(window) if window else 0, *rest))
+            self._check(self.lib.idm_attention_tc_biased(_p(q), _p(out), _p(sink), _p(slopes), int(window) if window else 0,
+                                                         float(softcap or 0.0), int(keep_first or 0), *rest))
         elif sink is None:
             self._check(self.lib.idm_attention_tc(_p(q), _p(out), *rest))
         else:

@@ -112,9 +112,10 @@ class HeadAttention(Mixer):
                           s.n_heads, s.n_kv_heads, s.key_dim, s.value_dim, self.biases, self.gammas, s.eps, cs,
                           self.magnitude, kv, ctx)
         gate = proj[:, col0 + self.col_gate:] if s.head_gate else None
-        if K.attention_tc_fits(kv, s.key_dim, s.value_dim) and s.softmax_scale > 0 and not self.keep_first and not self.softcap:
+        if K.attention_tc_fits(kv, s.key_dim, s.value_dim) and s.softmax_scale > 0:
             # on the tensor cores, for prompts and single tokens alike; gate and constant in a pass of their own
-            o = K.attention_tc(q, kv, ctx, s.softmax_scale, sink=self.sink, slopes=self.slopes, window=s.window)
+            o = K.attention_tc(q, kv, ctx, s.softmax_scale, sink=self.sink, slopes=self.slopes, window=s.window,
+                               softcap=self.softcap, keep_first=self.keep_first)
             K.gate_scale(o, gate, proj.shape[1], out_scale, out, out_col, gate_group=s.value_dim)
         else:
             K.attention_biased(q, kv, ctx, s.softmax_scale, out, out_col, out_scale, sink=self.sink, slopes=self.slopes,

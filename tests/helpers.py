@@ -398,3 +398,138 @@ def make_fuginex_dir(cfg: dict, out_dir: str, seed: int = 1, dtype=torch.bfloat1
         del f
         write_safetensors(path, tensors)
     return out_dir
+
+
+# ------------------------------------------------------------------------------------- Pununex
+def pununex_delta(heads=4, kv_heads=2, dim=16, vdim=24, conv=3, mlp="dense"):
+    """One ``delta`` layer of a Pununex config.json; ``mlp``: None, "dense", an inner size, or a dict as config.json has it."""
+    return dict(type="delta", mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, conv=conv), mlp=pununex_mlp(mlp))
+
+
+def pununex_parallel(heads=4, kv_heads=2, dim=24, vdim=16, scale=0.25, softcap=10.0, window=20, keep_first=3, r_heads=2,
+                     r_kv_heads=1, r_dim=12, r_vdim=20, conv=4, left_scale=1.3, right_scale=0.6, mlp="moe"):
+    """One ``parallel`` layer; absent options (no cap, no window, no kept tokens) are left out of the dict."""
+    left = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale)
+    if softcap:
+        left["softcap"] = softcap
+    if window:
+        left["mask"] = dict(size=window)
+        if keep_first:
+            left["mask"]["keep_first"] = keep_first
+    right = dict(heads=r_heads, kv_heads=r_kv_heads, dim=r_dim, vdim=r_vdim, conv=conv)
+    return dict(type="parallel", mixer=dict(left=left, right=right, left_scale=left_scale, right_scale=right_scale),
+                mlp=pununex_mlp(mlp))
+
+
+def pununex_moe(experts=6, identity=2, top=3, groups=(4, 2), scale=1.5, ff=24, shared=40):
+    router = dict(experts=experts, top=top, scale=scale)
+    if identity:
+        router["identity"] = identity
+    if groups:
+        router["groups"] = dict(count=groups[0], keep=groups[1])
+    d = dict(kind="moe", expert=dict(ff=ff), router=router)
+    if shared:
+        d["shared"] = dict(ff=shared)
+    return d
+
+
+def pununex_mlp(mlp):
+    if mlp is None or isinstance(mlp, dict):
+        return mlp
+    if mlp == "dense":
+        return dict(kind="dense", ff=48)
+    if mlp == "moe":
+        return pununex_moe()
+    return dict(kind="dense", ff=int(mlp))
+
+
+def pununex_config(layers, vocab=97, width=32, eps=1e-5, bigram=(53, 5, 11)):
+    import copy
+    d = dict(architecture="Pununex", vocab=vocab, width=width, norm=dict(eps=eps), layers=[copy.deepcopy(L) for L in layers])
+    if bigram:
+        d["embedding"] = dict(bigram=dict(buckets=bigram[0], mul_prev=bigram[1], mul_cur=bigram[2]))
+    return d
+
+
+# Small Pununex models that differ from one another in every size and option.
+PUNUNEX = {
+    # both kinds of layer in both orders, grouped heads on every side, a window shorter than a page with kept first
+    # tokens, experts in groups with identity experts and a shared expert, a dense feed-forward
+    "A": lambda: pununex_config([pununex_delta(), pununex_parallel(), pununex_parallel(mlp="dense", window=33, keep_first=1),
+                                 pununex_delta(mlp="moe")]),
+    # values of 1 and absent options: one head everywhere, no cap, no window, one tap, constants of 1, one expert per
+    # token, no identity experts, no groups, no shared expert, a layer without feed-forward, no bigram table
+    "B": lambda: pununex_config([pununex_parallel(heads=1, kv_heads=1, dim=8, vdim=8, softcap=None, window=None, r_heads=1,
+                                                  r_kv_heads=1, r_dim=8, r_vdim=8, conv=1, left_scale=1.0, right_scale=1.0,
+                                                  mlp=pununex_moe(experts=3, identity=0, top=1, groups=None, scale=1.0, shared=None)),
+                                 pununex_delta(heads=1, kv_heads=1, dim=8, vdim=8, conv=2, mlp=None)], vocab=50, width=24, bigram=None),
+    # widths that are no multiple of 8 (bfloat16 rows off the 16-byte borders), a window of one page and one key that
+    # keeps a whole page, groups that shut nobody out, multipliers larger than the table (two layers:
+    # rows of 20 elements round coarsely in bfloat16, and every norm behind a sublayer blows that up again)
+    "C": lambda: pununex_config([pununex_parallel(heads=3, kv_heads=1, dim=12, vdim=6, scale=0.2, softcap=4.0, window=65, keep_first=64,
+                                                  r_heads=3, r_kv_heads=3, r_dim=10, r_vdim=6, conv=2,
+                                                  mlp=pununex_moe(experts=5, identity=1, top=2, groups=(3, 3), scale=0.7, ff=12, shared=20)),
+                                 pununex_delta(heads=3, kv_heads=1, dim=10, vdim=12, conv=4, mlp=60)], vocab=33, width=20, eps=1e-6,
+                                bigram=(7, 1000003, 999983)),
+    # head sizes the tensor-core attention has, keys of 128 and values of 64 in the recurrences, many experts
+    "T": lambda: pununex_config([pununex_parallel(heads=4, kv_heads=1, dim=64, vdim=64, scale=0.12, softcap=30.0, window=100, keep_first=5,
+                                                  r_heads=2, r_kv_heads=1, r_dim=128, r_vdim=64, conv=4,
+                                                  mlp=pununex_moe(experts=16, identity=0, top=2, groups=(2, 1), scale=2.5, ff=32, shared=64)),
+                                 pununex_delta(heads=2, kv_heads=2, dim=64, vdim=128, conv=4, mlp=96),
+                                 pununex_parallel(heads=2, kv_heads=2, dim=128, vdim=128, scale=0.09, softcap=None, window=70, keep_first=70,
+                                                  r_heads=4, r_kv_heads=4, r_dim=32, r_vdim=32, conv=3, mlp=None)], vocab=211, width=64,
+                                bigram=(211, 31, 1)),
+}
+
+
+def pununex_random_config(seed: int) -> dict:
+    """A Pununex configuration drawn from sizes a model of the design may have: one to four layers of both kinds in any
+    order, grouped and ungrouped heads, windows below, at and above a page with none to many kept tokens, caps, filters
+    of 1 to 4 taps, feed-forwards of every kind."""
+    import random
+    r = random.Random(seed)
+
+    def mlp():
+        kind = r.choice(["none", "dense", "moe", "moe"])
+        if kind == "none":
+            return None
+        if kind == "dense":
+            return r.choice([64, 160])
+        count = r.choice([1, 2, 4])
+        per = r.choice([2, 3, 4])
+        identity = r.choice([0, 1, 2])
+        keep = r.randint(1, count)
+        return pununex_moe(experts=count * per - identity, identity=identity, top=r.randint(1, min(3, keep * per)),
+                           groups=None if count == 1 and r.random() < 0.5 else (count, keep), scale=r.choice([1.0, 2.0, 0.5]),
+                           ff=r.choice([16, 40, 64]), shared=r.choice([None, 32, 72]))
+
+    def layer():
+        if r.random() < 0.4:
+            kv = r.choice([1, 2])
+            return pununex_delta(heads=kv * r.choice([1, 2]), kv_heads=kv, dim=r.choice([16, 32, 40, 64, 128]),
+                                 vdim=r.choice([16, 24, 32, 64]), conv=r.choice([1, 2, 3, 4]), mlp=mlp())
+        kv = r.choice([1, 2, 4]); dim = r.choice([32, 48, 64, 128]); rkv = r.choice([1, 2, 4])
+        window = r.choice([None, 7, 64, 70, 129, 200])
+        return pununex_parallel(heads=kv * r.choice([1, 2, 4]), kv_heads=kv, dim=dim, vdim=r.choice([dim, 16, 40, 64]),
+                                scale=r.choice([dim ** -0.5, 0.1, 0.2]), softcap=r.choice([None, 5.0, 20.0, 50.0]), window=window,
+                                keep_first=r.choice([0, 1, 4, 33, 64, 90]) if window else 0, r_heads=rkv * r.choice([1, 2]),
+                                r_kv_heads=rkv, r_dim=r.choice([16, 32, 40, 64, 128]), r_vdim=r.choice([16, 24, 32, 64, 128]),
+                                conv=r.choice([1, 2, 3, 4]), left_scale=r.choice([1.0, 1.3, 0.4]),
+                                right_scale=r.choice([1.0, 0.8, 0.7]), mlp=mlp())
+    V = r.choice([128, 500, 1000])
+    return pununex_config([layer() for _ in range(r.choice([1, 2, 3, 4]))], vocab=V, width=r.choice([64, 96, 128, 256]),
+                          eps=r.choice([1e-5, 1e-6]), bigram=r.choice([None, (V - 1, 3, 7), (2003, 40503, 12289)]))
+
+
+def make_pununex_dir(cfg: dict, out_dir: str, seed: int = 1, dtype=torch.bfloat16, std: float = 0.15, edit=None) -> str:
+    """A Pununex model folder with seeded random weights; ``edit(name, tensor) -> tensor`` may change them."""
+    from idempotent_llm_b200.config import PununexConfig
+    from idempotent_llm_b200.weights import write_random_model, write_safetensors, SafetensorsFile
+    write_random_model(PununexConfig.from_dict(cfg), out_dir, seed=seed, dtype=dtype, std=std)
+    if edit is not None:
+        path = os.path.join(out_dir, "model.safetensors")
+        f = SafetensorsFile(path)
+        tensors = [(n, edit(n, f.get(n).clone())) for n in f.names()]
+        del f
+        write_safetensors(path, tensors)
+    return out_dir

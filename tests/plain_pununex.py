@@ -213,11 +213,45 @@ def route(z: torch.Tensor, correction: torch.Tensor, r: dict):
     return chosen, weights
 
 
-def routed_ff(h, w, p, c):
+def route_margin(z: torch.Tensor, correction: torch.Tensor, r: dict) -> torch.Tensor:
+    """[T]: how far each token's choice is from falling another way: the gap between the last chosen expert's choice
+    score and the best one not chosen (among the open groups), and, where groups shut experts out, the gap between the
+    last kept group's score and the best one shut out; the smaller of the two."""
+    E, top = z.shape[1], int(r["top"])
+    choice = torch.softmax(z, dim=-1) + correction
+    groups = r.get("groups") or {}
+    count, keep = int(groups.get("count") or 1), int(groups.get("keep") or groups.get("count") or 1)
+    margin = torch.full((z.shape[0],), math.inf, dtype=z.dtype)
+    if count > 1 and keep < count:
+        per = E // count
+        best = choice.view(-1, count, per).max(dim=-1).values.sort(dim=-1, descending=True).values
+        margin = best[:, keep - 1] - best[:, keep]
+        kept = choice.view(-1, count, per).max(dim=-1).values.topk(keep, dim=-1).indices
+        allowed = torch.zeros(z.shape[0], count, dtype=torch.bool).scatter_(1, kept, True)
+        choice = choice.masked_fill(~allowed[:, :, None].expand(-1, -1, per).reshape(-1, E), -math.inf)
+    ranked = choice.sort(dim=-1, descending=True).values
+    if top < E:
+        margin = torch.minimum(margin, ranked[:, top - 1] - ranked[:, top])
+    return margin
+
+
+def routed_ff(h, w, p, c, forced=None, flips=None):
+    """``forced`` [T, top]: the experts every token is given instead of the router's own choice (the weights still come
+    from this function's own softmax); ``flips`` then receives (token, margin of the own choice) wherever the given
+    experts are not the own ones.  For comparisons in low precision, where a choice within rounding may fall either way."""
     r = c["router"]
     n_real, n_id = int(r["experts"]), int(r.get("identity") or 0)
     z = h @ w[p + "router"].T
     chosen, weights = route(z, w[p + "correction"], r)
+    if forced is not None:
+        own, margin = chosen, route_margin(z, w[p + "correction"], r)
+        chosen = forced.long()
+        picked = torch.softmax(z, dim=-1).gather(1, chosen)
+        weights = picked / (picked.sum(dim=-1, keepdim=True) + 1e-20) * float(r.get("scale", 1.0))
+        if flips is not None:
+            for t in range(h.shape[0]):
+                if sorted(own[t].tolist()) != sorted(chosen[t].tolist()):
+                    flips.append((t, float(margin[t])))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, wt in zip(chosen[t].tolist(), weights[t]):
@@ -230,11 +264,11 @@ def routed_ff(h, w, p, c):
     return out
 
 
-def feed_forward(h, w, p, c):
+def feed_forward(h, w, p, c, forced=None, flips=None):
     if c["kind"] == "dense":
         return gated_ff(h, w, p, torch.relu)
     if c["kind"] == "moe":
-        return routed_ff(h, w, p, c)
+        return routed_ff(h, w, p, c, forced, flips)
     raise ValueError(c["kind"])
 
 
@@ -272,8 +306,10 @@ def load(model_dir: str):
     return cfg, out
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], layers_out: Optional[list] = None) -> torch.Tensor:
-    """Logits [T, vocab] of one sequence; ``layers_out`` receives the stream after every layer."""
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], layers_out: Optional[list] = None,
+            routes: Optional[dict] = None, flips: Optional[list] = None) -> torch.Tensor:
+    """Logits [T, vocab] of one sequence; ``layers_out`` receives the stream after every layer.  ``routes`` {layer: [T,
+    top]} gives routed layers their experts (see ``routed_ff``); ``flips`` receives (layer, token, margin)."""
     eps = float(cfg["norm"]["eps"])
     x = embed(tokens, w, cfg)
     for i, L in enumerate(cfg["layers"]):
@@ -286,7 +322,11 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], layers
             raise ValueError(L["type"])
         x = x + w[p + "ls1"] * layer_norm(y, w[p + "norm1"], w[p + "norm1.b"], eps)
         if L.get("mlp"):
-            y = feed_forward(x, w, p + "mlp.", L["mlp"])
+            mine = []
+            forced = None if routes is None or i not in routes else routes[i][:len(tokens)]
+            y = feed_forward(x, w, p + "mlp.", L["mlp"], forced, mine)
+            if flips is not None:
+                flips += [(i, t, m) for t, m in mine]
             x = x + w[p + "ls2"] * layer_norm(y, w[p + "norm2"], w[p + "norm2.b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
