@@ -101,8 +101,8 @@ HEAD_VARIANTS = {
     # no sink: the cap and the kept tokens alone
     "no_sink": lambda: _head_spec(window=30, keep_first=3, softcap=4.0, sink=False),
     # head sizes the tensor cores have
-    "capped_64": lambda: _head_spec(n_heads=4, n_kv_heads=1, key_dim=64, value_dim=64, softmax_scale=0.15, window=100, keep_first=6,
-                                    softcap=20.0),
+    "capped_64": lambda: _head_spec(n_heads=4, n_kv_heads=2, key_dim=64, value_dim=64, softmax_scale=0.15, window=100, keep_first=7,
+                                    softcap=25.0),
     "capped_128_long": lambda: _head_spec(n_heads=2, n_kv_heads=1, key_dim=128, value_dim=128, softmax_scale=0.09, window=700,
                                           keep_first=70, softcap=30.0),
 }
@@ -273,7 +273,7 @@ def test_delta_rule_alone_in_portions(dtype, variant):
 # ----------------------------------------------------------------------------------- router and experts, alone
 ROUTER_SHAPES = [
     # experts (identity experts among them), per token, groups, kept groups
-    (14, 2, 2, 1), (7, 3, 1, 1), (64, 6, 8, 3), (3, 3, 1, 1), (12, 4, 4, 4), (40, 1, 5, 1), (96, 8, 3, 2), (2, 1, 2, 1),
+    (18, 2, 3, 1), (7, 3, 1, 1), (64, 6, 8, 3), (3, 3, 1, 1), (12, 4, 4, 4), (40, 1, 5, 1), (96, 8, 3, 2), (2, 1, 2, 1),
 ]
 
 
