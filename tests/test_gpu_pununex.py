@@ -817,6 +817,45 @@ def test_greedy_generation_through_the_entry_point(pununex_dirs):
             lg = eager.engine.step([(s, [t])])
 
 
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("T", "bfloat16")])
+def test_the_device_side_decode_loop_gives_the_tokens_generation_gives(pununex_dirs, name, dtype):
+    """``Engine.decode_session`` (model, greedy pick and feedback in one captured graph): the embedding's bigram row is
+    hashed from a token that was chosen on the device one replay earlier and never seen by the host."""
+    d = pununex_dirs(name, dtype)
+    lm = api.load(d, dtype=dtype, max_tokens=64 * 24, max_seqs=8)
+    eng = lm.engine
+    prompts = [helpers.rand_ids(n, lm.spec.vocab_size, 500 + n) for n in (5, 61, 30)]
+    steps = 70
+    toks, _ = lm.generate(prompts, steps)
+    assert eng.cache.slots.n_held == 0 and eng.cache.pages_held() == 0
+    slots = [eng.open() for _ in prompts]
+    first = eng.sample(eng.step(list(zip(slots, prompts))), 0.0, 0, list(range(len(prompts))), [0] * len(prompts))
+    assert first == toks[:, 0].tolist()
+    sess = eng.decode_session(slots, first, steps - 1)
+    sess.run(steps - 1)
+    got = sess.tokens()
+    sess.finish()
+    assert torch.equal(got.T.long(), toks[:, 1:].long()), "the device-side loop chose other tokens than generation"
+    if dtype == "float32":                                     # and the sequences go on from where the session left them
+        more = eng.step([(s, [int(t)]) for s, t in zip(slots, got[-1])])
+        whole = torch.stack([_plain_logits(d, list(p) + toks[i].tolist())[-1] for i, p in enumerate(prompts)])
+        assert helpers.rel_err(more, whole) < TOL[dtype]
+    for s in slots:
+        eng.close(s)
+
+
+def test_sampling_with_a_temperature_is_the_same_in_any_batch(pununex_dirs):
+    """Tokens drawn at temperature 0.8 for a request alone and beside two others: the same (the draw is keyed by seed,
+    request and step; the logits do not depend on the batch beyond rounding, which no draw here rests on)."""
+    d = pununex_dirs("A", "float32")
+    lm = api.load(d, dtype="float32", max_tokens=512)
+    V = lm.spec.vocab_size
+    prompts = [helpers.rand_ids(n, V, 90 + n) for n in (7, 2, 33)]
+    together = lm.generate_requests(prompts, 12, temperature=0.8, seed=5)
+    alone = lm.generate_requests(prompts[:1], 12, temperature=0.8, seed=5)
+    assert together[0].tokens == alone[0].tokens and len(set(together[0].tokens)) > 3
+
+
 def test_the_command_line_replays_a_trace(pununex_dirs, tmp_path):
     """``bin/trace_run`` on a Pununex folder: whole, decoded and batched give the plain implementation's logits."""
     import json
